@@ -1,0 +1,307 @@
+"""Operator API of the reference's `clusterfusion` module for the Pythia decode path.
+
+Same names, positional order and return values as the pybind table of the
+reference (include/pybind.cpp:285-297); each function validates its tensors
+(the reference validates nothing) and forwards raw pointers to the C ABI on
+torch's current stream.  No computation happens in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Tuple
+
+import torch
+
+from . import _lib
+from ._lib import CF_PYTHIA_2B8, CF_PYTHIA_6B9, CfLayerIO, CfLayerWeights, CfStepArgs, check, lib
+
+_DIMS = {}
+
+
+def model_dims(model: int) -> _lib.CfDims:
+    if model not in _DIMS:
+        d = _lib.CfDims()
+        check(lib.cf_model_dims(model, C.byref(d)))
+        _DIMS[model] = d
+    return _DIMS[model]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _req(t: torch.Tensor, name: str, numel: int, dtype=torch.float16, exact: bool = True) -> int:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name}: expected a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: expected a CUDA tensor, got {t.device}")
+    if t.device.index != torch.cuda.current_device():
+        raise RuntimeError(f"{name}: tensor is on {t.device} but the current device is cuda:{torch.cuda.current_device()}")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name}: expected a contiguous tensor")
+    if (exact and t.numel() != numel) or (not exact and t.numel() < numel):
+        raise RuntimeError(f"{name}: expected {'' if exact else 'at least '}{numel} elements, got shape {tuple(t.shape)}")
+    if t.data_ptr() % 16 != 0:
+        raise RuntimeError(f"{name}: storage must be 16-byte aligned")
+    return t.data_ptr()
+
+
+def _cache(t: torch.Tensor, name: str, width: int) -> Tuple[int, int]:
+    if not isinstance(t, torch.Tensor) or t.dim() != 2 or t.shape[1] != width:
+        raise RuntimeError(f"{name}: expected a [rows, {width}] tensor")
+    ptr = _req(t, name, t.numel())
+    return ptr, t.shape[0]
+
+
+def _weights(d, weight_qkv, bias_qkv, weight_o, bias_o, ln_w, ln_b, pln_w, pln_b, up_w, up_b, down_w, down_b):
+    H, KVW, F = d.hidden, d.heads * d.head_dim, d.ffn
+    w = CfLayerWeights()
+    w.qkv_weight = _req(weight_qkv, "weight_qkv", 3 * KVW * H)
+    w.qkv_bias = _req(bias_qkv, "bias_qkv", 3 * KVW)
+    w.o_weight = _req(weight_o, "weight_o", H * KVW)
+    w.o_bias = _req(bias_o, "bias_o", H)
+    w.ln_weight = _req(ln_w, "layernorm_weight", H)
+    w.ln_bias = _req(ln_b, "layernorm_bias", H)
+    w.post_ln_weight = _req(pln_w, "post_ln_weight", H)
+    w.post_ln_bias = _req(pln_b, "post_ln_bias", H)
+    w.mlp_up_weight = _req(up_w, "mlp_up_weight", F * H)
+    w.mlp_up_bias = _req(up_b, "mlp_up_bias", F)
+    if down_w is not None:
+        w.mlp_down_weight = _req(down_w, "mlp_down_weight", H * F)
+        w.mlp_down_bias = _req(down_b, "mlp_down_bias", H)
+    return w
+
+
+def _layer_call(model, fn, input, weight_qkv, bias_qkv, weight_o, bias_o, k_cache, v_cache, layernorm_weight,
+                layernorm_bias, cos, sin, post_ln_weight, post_ln_bias, mlp_up_weight, mlp_up_bias,
+                mlp_down_weight, mlp_down_bias, current_seq_len):
+    d = model_dims(model)
+    H, NH, D = d.hidden, d.heads, d.head_dim
+    w = _weights(d, weight_qkv, bias_qkv, weight_o, bias_o, layernorm_weight, layernorm_bias, post_ln_weight,
+                 post_ln_bias, mlp_up_weight, mlp_up_bias, mlp_down_weight, mlp_down_bias)
+    io = CfLayerIO()
+    io.input = _req(input, "input", H)
+    io.k_cache, rows_k = _cache(k_cache, "k_cache", NH * D)
+    io.v_cache, rows_v = _cache(v_cache, "v_cache", NH * D)
+    if rows_k != rows_v:
+        raise RuntimeError("k_cache and v_cache must have the same number of rows")
+    io.kv_rows = rows_k
+    io.cos = _req(cos, "cos", d.rotary, torch.float32, exact=False)
+    io.sin = _req(sin, "sin", d.rotary, torch.float32, exact=False)
+    opts = dict(dtype=torch.float16, device=input.device)
+    out = torch.empty((1, H), **opts)
+    k = torch.empty((1, NH, D), **opts)
+    v = torch.empty((1, NH, D), **opts)
+    io.output, io.k_new, io.v_new = out.data_ptr(), k.data_ptr(), v.data_ptr()
+    check(fn(model, C.byref(w), C.byref(io), int(current_seq_len), _stream()))
+    return out, k, v
+
+
+def pythia_2b8_decoder_layer(*args):
+    """(output[1,2560], k_new[1,32,80], v_new[1,32,80]); writes row current_seq_len of both caches.
+    Reference: pythia_2b8_decoder_layer_sm120, include/pybind.cpp:109-129,285."""
+    return _layer_call(CF_PYTHIA_2B8, lib.cf_pythia_decoder_layer, *args)
+
+
+def pythia_6b9_decoder_layer(*args):
+    """(output[1,4096], k_new[1,32,128], v_new[1,32,128]); writes row current_seq_len of both caches.
+    Reference: pythia_6b9_decoder_layer_sm120, include/pybind.cpp:198-218,294."""
+    return _layer_call(CF_PYTHIA_6B9, lib.cf_pythia_decoder_layer, *args)
+
+
+def pythia_2b8_decoder_layer_split(*args):
+    """Two launches, same bits as pythia_2b8_decoder_layer.
+    Reference: pythia_2b8_decoder_layer_split_sm120, include/pybind.cpp:132-151,286."""
+    return _layer_call(CF_PYTHIA_2B8, lib.cf_pythia_decoder_layer_split, *args)
+
+
+def pythia_6b9_decoder_layer_split(*args):
+    """Split launch for the 6.9B shapes (the reference only ships the 2.8B one)."""
+    return _layer_call(CF_PYTHIA_6B9, lib.cf_pythia_decoder_layer_split, *args)
+
+
+def pythia_2b8_attention_only(input, weight_qkv, bias_qkv, weight_o, bias_o, k_cache, v_cache, layernorm_weight,
+                              layernorm_bias, cos, sin, post_ln_weight, post_ln_bias, mlp_up_weight, mlp_up_bias,
+                              current_seq_len):
+    """(attn_output[1,H], mlp_intermediate[F], k_new, v_new).
+    Reference: pythia_2b8_attention_only_sm120, include/pybind.cpp:154-171,287."""
+    model = CF_PYTHIA_2B8
+    d = model_dims(model)
+    H, NH, D = d.hidden, d.heads, d.head_dim
+    w = _weights(d, weight_qkv, bias_qkv, weight_o, bias_o, layernorm_weight, layernorm_bias, post_ln_weight,
+                 post_ln_bias, mlp_up_weight, mlp_up_bias, None, None)
+    io = CfLayerIO()
+    io.input = _req(input, "input", H)
+    io.k_cache, rows_k = _cache(k_cache, "k_cache", NH * D)
+    io.v_cache, rows_v = _cache(v_cache, "v_cache", NH * D)
+    if rows_k != rows_v:
+        raise RuntimeError("k_cache and v_cache must have the same number of rows")
+    io.kv_rows = rows_k
+    io.cos = _req(cos, "cos", d.rotary, torch.float32, exact=False)
+    io.sin = _req(sin, "sin", d.rotary, torch.float32, exact=False)
+    opts = dict(dtype=torch.float16, device=input.device)
+    attn = torch.empty((1, H), **opts)
+    mid = torch.empty((d.ffn,), **opts)
+    k = torch.empty((1, NH, D), **opts)
+    v = torch.empty((1, NH, D), **opts)
+    io.attn_output, io.mlp_intermediate = attn.data_ptr(), mid.data_ptr()
+    io.k_new, io.v_new = k.data_ptr(), v.data_ptr()
+    check(lib.cf_pythia_attention_only(model, C.byref(w), C.byref(io), int(current_seq_len), _stream()))
+    return attn, mid, k, v
+
+
+def pythia_2b8_mlp_only(input, attn_output, mlp_intermediate, mlp_down_weight, mlp_down_bias):
+    """output[1,H] = input + attn_output + down(mlp_intermediate) + bias.
+    Reference: pythia_2b8_mlp_only_sm120, include/pybind.cpp:174-180,288."""
+    model = CF_PYTHIA_2B8
+    d = model_dims(model)
+    H, F = d.hidden, d.ffn
+    out = torch.empty((1, H), dtype=torch.float16, device=input.device)
+    check(lib.cf_pythia_mlp_only(
+        model, _req(input, "input", H), _req(attn_output, "attn_output", H),
+        _req(mlp_intermediate, "mlp_intermediate", F), _req(mlp_down_weight, "mlp_down_weight", H * F),
+        _req(mlp_down_bias, "mlp_down_bias", H), out.data_ptr(), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------- contexts
+class _DeviceView:
+    """Zero-copy torch view of a buffer the C library owns."""
+
+    def __init__(self, ptr: int, shape, typestr="<f2"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _wrap(ptr: int, shape, device) -> torch.Tensor:
+    return torch.as_tensor(_DeviceView(ptr, shape), device=device)
+
+
+_ctx_keepalive = {}  # (model, id) -> tensors the context points at
+_ctx_views = {}      # (model, id) -> (out, k_new, v_new) views of the static buffers
+
+
+def _create(model, context_id, k_cache, v_cache, weight_qkv, weight_o, mlp_up_weight, mlp_down_weight, max_seq_len):
+    d = model_dims(model)
+    H, KVW, F = d.hidden, d.heads * d.head_dim, d.ffn
+    kp, rows_k = _cache(k_cache, "k_cache", KVW)
+    vp, rows_v = _cache(v_cache, "v_cache", KVW)
+    max_seq_len = int(max_seq_len)
+    if max_seq_len <= 0 or max_seq_len > min(rows_k, rows_v):
+        raise RuntimeError(f"max_seq_len {max_seq_len} exceeds the cache rows ({rows_k}, {rows_v})")
+    check(lib.cf_pythia_create_graph_context(
+        model, int(context_id), kp, vp, _req(weight_qkv, "weight_qkv", 3 * KVW * H),
+        _req(weight_o, "weight_o", H * KVW), _req(mlp_up_weight, "mlp_up_weight", F * H),
+        _req(mlp_down_weight, "mlp_down_weight", H * F), max_seq_len))
+    key = (model, int(context_id))
+    _ctx_keepalive[key] = (k_cache, v_cache, weight_qkv, weight_o, mlp_up_weight, mlp_down_weight)
+    _ctx_views.pop(key, None)
+
+
+def _step(model, context_id, input, layernorm_weight, layernorm_bias, qkv_bias, o_bias, cos, sin, k_cache, v_cache,
+          post_ln_weight, post_ln_bias, mlp_up_bias, mlp_down_bias, current_seq_len):
+    d = model_dims(model)
+    H, NH, D, KVW, F = d.hidden, d.heads, d.head_dim, d.heads * d.head_dim, d.ffn
+    a = CfStepArgs()
+    a.input = _req(input, "input", H)
+    a.ln_weight = _req(layernorm_weight, "layernorm_weight", H)
+    a.ln_bias = _req(layernorm_bias, "layernorm_bias", H)
+    a.qkv_bias = _req(qkv_bias, "qkv_bias", 3 * KVW)
+    a.o_bias = _req(o_bias, "o_bias", H)
+    a.cos = _req(cos, "cos", d.rotary, torch.float32, exact=False)
+    a.sin = _req(sin, "sin", d.rotary, torch.float32, exact=False)
+    a.k_cache, _ = _cache(k_cache, "k_cache", KVW)
+    a.v_cache, _ = _cache(v_cache, "v_cache", KVW)
+    a.post_ln_weight = _req(post_ln_weight, "post_ln_weight", H)
+    a.post_ln_bias = _req(post_ln_bias, "post_ln_bias", H)
+    a.mlp_up_bias = _req(mlp_up_bias, "mlp_up_bias", F)
+    a.mlp_down_bias = _req(mlp_down_bias, "mlp_down_bias", H)
+    po, pk, pv = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    check(lib.cf_pythia_graph_decode_step(model, int(context_id), C.byref(a), int(current_seq_len), _stream(),
+                                          C.byref(po), C.byref(pk), C.byref(pv)))
+    key = (model, int(context_id))
+    views = _ctx_views.get(key)
+    if views is None:
+        dev = input.device
+        views = (_wrap(po.value, (1, H), dev), _wrap(pk.value, (1, NH, D), dev), _wrap(pv.value, (1, NH, D), dev))
+        _ctx_views[key] = views
+    return views
+
+
+def _destroy(model, context_id):
+    check(lib.cf_pythia_destroy_graph_context(model, int(context_id)))
+    key = (model, int(context_id))
+    _ctx_keepalive.pop(key, None)
+    _ctx_views.pop(key, None)
+
+
+def _set_device_state(model, context_id, seq_len_dev, cos_table, sin_table):
+    d = model_dims(model)
+    sp = 0 if seq_len_dev is None else _req(seq_len_dev, "seq_len_dev", 1, torch.int32)
+    cp = sp_ = 0
+    stride = 0
+    if cos_table is not None:
+        if cos_table.dim() != 2 or cos_table.shape[1] < d.rotary or cos_table.shape != sin_table.shape:
+            raise RuntimeError("cos_table / sin_table: expected matching [rows, >= rotary] fp32 tensors")
+        cp = _req(cos_table, "cos_table", cos_table.numel(), torch.float32)
+        sp_ = _req(sin_table, "sin_table", sin_table.numel(), torch.float32)
+        stride = cos_table.shape[1]
+    check(lib.cf_pythia_graph_set_device_state(model, int(context_id), sp, cp, sp_, stride))
+    _ctx_keepalive[(model, int(context_id), "dev")] = (seq_len_dev, cos_table, sin_table)
+
+
+def pythia_2b8_create_graph_context(*a):
+    """Reference: pythia_2b8_create_graph_context_sm120, include/pybind.cpp:206-215,289."""
+    _create(CF_PYTHIA_2B8, *a)
+
+
+def pythia_2b8_graph_decode_step(*a):
+    """Returns views of the context's static buffers (clone to keep).
+    Reference: pythia_2b8_graph_decode_step_sm120, include/pybind.cpp:217-233,290."""
+    return _step(CF_PYTHIA_2B8, *a)
+
+
+def pythia_2b8_destroy_graph_context(context_id):
+    """Reference: pythia_2b8_destroy_graph_context_sm120, include/pybind.cpp:235,291."""
+    _destroy(CF_PYTHIA_2B8, context_id)
+
+
+def pythia_6b9_create_graph_context(*a):
+    """Reference: pythia_6b9_create_graph_context_sm120, include/pybind.cpp:238-247,295."""
+    _create(CF_PYTHIA_6B9, *a)
+
+
+def pythia_6b9_graph_decode_step(*a):
+    """Reference: pythia_6b9_graph_decode_step_sm120, include/pybind.cpp:249-265,296."""
+    return _step(CF_PYTHIA_6B9, *a)
+
+
+def pythia_6b9_destroy_graph_context(context_id):
+    """Reference: pythia_6b9_destroy_graph_context_sm120, include/pybind.cpp:267,297."""
+    _destroy(CF_PYTHIA_6B9, context_id)
+
+
+def pythia_2b8_graph_set_device_state(context_id, seq_len_dev, cos_table=None, sin_table=None):
+    """Extension: let a context read seq_len (int32 tensor) and its RoPE row from device
+    memory so a captured CUDA graph of graph_decode_step calls can be replayed."""
+    _set_device_state(CF_PYTHIA_2B8, context_id, seq_len_dev, cos_table, sin_table)
+
+
+def pythia_6b9_graph_set_device_state(context_id, seq_len_dev, cos_table=None, sin_table=None):
+    _set_device_state(CF_PYTHIA_6B9, context_id, seq_len_dev, cos_table, sin_table)
+
+
+def device_status() -> int:
+    """Synchronise and return the device status word (0 = every launch completed normally);
+    raises RuntimeError if a kernel reported a timeout or a bad sequence length."""
+    s = C.c_int(0)
+    check(lib.cf_get_status(C.byref(s)))
+    return s.value
+
+
+def launch_info(model: int = CF_PYTHIA_6B9) -> dict:
+    v = [C.c_int(0) for _ in range(5)]
+    check(lib.cf_launch_info(model, *[C.byref(x) for x in v]))
+    return dict(sm_count=v[0].value, grid=v[1].value, cluster=v[2].value, stages=v[3].value, smem_bytes=v[4].value)

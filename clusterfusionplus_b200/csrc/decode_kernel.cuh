@@ -1,0 +1,956 @@
+// Fused GPT-NeoX/Pythia decode step (batch 1) for sm_100a: one persistent,
+// co-resident grid that streams every weight and KV byte exactly once through a
+// TMA ring and keeps all reductions in fp32 and in a fixed order.
+//
+// It covers what the reference does in Pythia6b9DecoderLayerKernel
+// (include/5090/pythia_6b9/kernel.cuh:56-900) and PythiaDecoderLayerKernel
+// (include/5090/pythia_2b8/kernel.cuh:51-950), its split variants
+// (pythia_2b8/kernel_attention.cuh:51, kernel_mlp.cuh:29) and the decode-loop
+// tail the reference leaves to PyTorch (tests/benchmark_decode_6b9.py:186-195),
+// but is organised differently:
+//
+//   P1  LayerNorm (both norms share mean/rstd) -> {QKV, MLP-up} GEMV, output rows
+//       partitioned over ALL CTAs (no split-K), + bias (+ tanh-GELU for MLP-up)
+//   --- grid barrier ---
+//   P2  partial NeoX RoPE, KV append, flash-decode over (head, 64-row chunk)
+//       items spread evenly over all CTAs, per-CTA partial (m, l, acc) in fp32
+//   --- grid barrier ---
+//   P3  merge attention partials, {O-proj, MLP-down} as ONE GEMV over
+//       K = [attn ; mid]; K-chunks interleaved over the CTAs of a cluster and
+//       the partial rows summed through distributed shared memory
+//       (dsm.cuh), + biases + residual -> fp16 output
+//   P4  (optional tail) final LayerNorm -> LM-head GEMV -> argmax
+//
+// One producer thread issues every TMA load of the whole launch in program
+// order, limited only by ring capacity: it runs ahead of the consumers across
+// phase and layer boundaries, so the next phase's weights are already landing
+// while the consumers sit in a grid barrier.
+//
+// Determinism: no atomics on data; every sum has a fixed association order that
+// depends only on (grid size, cluster size, sequence length).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "dsm.cuh"
+#include "pipeline.cuh"
+
+namespace cfb {
+
+constexpr int KCHUNK = 256;                 // K elements per TMA box (512 B rows)
+constexpr int GRAN = 8;                     // rows per granule (one box = 8 x 256 fp16 = 4 KB)
+constexpr int SLOT_BYTES = GRAN * KCHUNK * 2;
+constexpr int NSLOT = 9;                    // granules per stage (warps 0..7 take slot w, warp 0 also slot 8)
+constexpr int STAGE_BYTES = NSLOT * SLOT_BYTES;  // 36 KB
+constexpr int MAX_STAGES = 8;
+constexpr int NCWARP = 8;                   // consumer warps
+constexpr int NCTHR = NCWARP * 32;          // consumer threads
+constexpr int NTHREADS = NCTHR + 32;        // + producer warp
+constexpr int KV_TILE = 64;                 // cache rows per attention item
+constexpr int MAXL = 4;                     // attention partial slots per CTA
+constexpr int MAX_P3_ROWS = 256;            // output rows one cluster may own in P3
+constexpr int MAX_H = 8192;                 // LayerNorm register staging limit
+
+enum : int { PH_P1 = 1, PH_P2 = 2, PH_P3 = 4, PH_P4 = 8 };
+enum : int {
+    F3_USE_O = 1,       // include W_o chunks (attention output) in P3
+    F3_USE_DOWN = 2,    // include W_down chunks (MLP) in P3
+    F3_ADD_X = 4,       // + residual input
+    F3_ADD_BO = 8,      // + o-proj bias
+    F3_ADD_BDOWN = 16,  // + mlp-down bias
+    F3_MID_F16 = 32,    // MLP intermediate comes from an fp16 tensor instead of fp32 scratch
+};
+
+// Per-layer descriptor, resident in device memory.
+struct alignas(128) LayerDesc {
+    CUtensorMap tm_qkv, tm_up, tm_o, tm_down, tm_k, tm_v;
+    const __half *ln_w, *ln_b, *pln_w, *pln_b;
+    const __half *b_qkv, *b_up, *b_o, *b_down;
+    __half *k_cache, *v_cache;
+    int kv_rows;  // rows in the cache allocation
+    int pad_[7];
+};
+
+struct alignas(128) TailDesc {
+    CUtensorMap tm_head;
+    const __half *fln_w, *fln_b;
+    int vocab;
+    int pad_[11];
+};
+
+struct Params {
+    const LayerDesc* layers;
+    const TailDesc* tail;
+    int n_layers;
+    int H;         // hidden size (K of P1, rows of P3)
+    int NH;        // heads held by this rank
+    int R;         // rotary dims
+    int F;         // MLP intermediate width held by this rank
+    int phase_mask;
+    int p3_flags;
+    int nstage;
+    int xbuf_floats;
+    // activations
+    const __half* x_in;   // [H]; ignored when embed != nullptr
+    const __half* embed;  // optional [V, H] table: x = embed[*token_in]
+    const int* token_in;
+    __half* out;          // output of the last layer of this launch
+    __half* hid[2];       // ping-pong hidden state between layers of one launch
+    __half* k_new;        // optional [NH*D] (single-layer launches)
+    __half* v_new;
+    const float* cos;     // row for this position, or table base when rope_stride > 0
+    const float* sin;
+    int rope_stride;      // floats between table rows; 0 = cos/sin point at the row itself
+    int seq_host;         // used when seq_ptr == nullptr
+    const int* seq_ptr;   // device-resident sequence length (graph replay)
+    // split-API tensors
+    __half* mid_f16_out;          // optional fp16 copy of the MLP intermediate
+    const __half* mid_f16_in;     // with F3_MID_F16
+    const __half* extra_add_f16;  // optional [H] added in the P3 epilogue
+    // scratch
+    float* qkv_f32;    // [3*NH*D]
+    float* mid_f32;    // [F]
+    float* attn_part;  // [grid][MAXL][D+2]
+    float* attn_new;   // [NH][D+2]
+    unsigned* sync;    // [0] barrier count, [1] exit count
+    int* status;
+    // tail outputs
+    float* logits;     // optional [vocab]
+    float* amax_val;   // [grid]
+    int* amax_idx;     // [grid]
+    int* token_out;    // next token id (may alias token_in)
+    int* seq_inc;      // optional: *seq_inc += 1 at the end of the launch
+    int vocab_offset;  // added to the argmax index (vocabulary shards)
+};
+
+__host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
+// units [part_begin(i), part_begin(i+1)) of `total` belong to part i of `parts`
+__host__ __device__ __forceinline__ int part_begin(int i, int total, int parts) {
+    return static_cast<int>((static_cast<long long>(i) * total) / parts);
+}
+// inverse of part_begin: which part owns unit t
+__host__ __device__ __forceinline__ int part_of(int t, int total, int parts) {
+    return static_cast<int>(((static_cast<long long>(t) + 1) * parts - 1) / total);
+}
+__host__ __device__ __forceinline__ int head_owner(int h, int NH, int G) { return part_begin(h, G, NH); }
+
+// ring cursor: same arithmetic on the producer and the consumer side
+struct Cursor {
+    int stage;
+    uint32_t phase;
+    int nstage;
+    __device__ __forceinline__ void advance() {
+        if (++stage == nstage) {
+            stage = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+struct Smem {
+    uint8_t* ring;
+    float* xbuf;
+    float* red;     // 64
+    float* q_s;     // 128
+    float* part_s;  // MAX_P3_ROWS
+    float* recv;    // MAX_P3_ROWS
+    uint64_t* full;
+    uint64_t* empty;
+    uint64_t* xbar;
+    int* abort_flag;
+};
+
+__host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
+    return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
+           (64 + 128 + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
+}
+
+__device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
+    Smem s;
+    s.ring = base;
+    s.xbuf = reinterpret_cast<float*>(base + static_cast<size_t>(nstage) * STAGE_BYTES);
+    s.red = s.xbuf + xbuf_floats;
+    s.q_s = s.red + 64;
+    s.part_s = s.q_s + 128;
+    s.recv = s.part_s + MAX_P3_ROWS;
+    s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
+    s.empty = s.full + MAX_STAGES;
+    s.xbar = s.empty + MAX_STAGES;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 1);
+    return s;
+}
+
+// ---------------------------------------------------------------- math helpers
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(u));
+}
+
+// 8 rows x 256 K of one slot against this lane's 8 activations
+__device__ __forceinline__ void gemv_slot(const uint8_t* slot, const float* xs, int lane, float (&acc)[GRAN]) {
+    const float4 xa = *reinterpret_cast<const float4*>(xs + lane * 8);
+    const float4 xb = *reinterpret_cast<const float4*>(xs + lane * 8 + 4);
+#pragma unroll
+    for (int r = 0; r < GRAN; ++r) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(slot + r * (KCHUNK * 2) + lane * 16);
+        const float2 w0 = __half22float2(*reinterpret_cast<const __half2*>(&wv.x));
+        const float2 w1 = __half22float2(*reinterpret_cast<const __half2*>(&wv.y));
+        const float2 w2 = __half22float2(*reinterpret_cast<const __half2*>(&wv.z));
+        const float2 w3 = __half22float2(*reinterpret_cast<const __half2*>(&wv.w));
+        float a = acc[r];
+        a = fmaf(w0.x, xa.x, a);
+        a = fmaf(w0.y, xa.y, a);
+        a = fmaf(w1.x, xa.z, a);
+        a = fmaf(w1.y, xa.w, a);
+        a = fmaf(w2.x, xb.x, a);
+        a = fmaf(w2.y, xb.y, a);
+        a = fmaf(w3.x, xb.z, a);
+        a = fmaf(w3.y, xb.w, a);
+        acc[r] = a;
+    }
+}
+
+// Sum 8 per-lane accumulators over the warp with 9 shuffles.  Afterwards lanes
+// with (lane & 3) == 0 hold the total of row ((lane>>4)&1)*4 + ((lane>>3)&1)*2 + ((lane>>2)&1).
+__device__ __forceinline__ float warp_reduce8(const float (&a)[GRAN], int lane) {
+    float b[4], c[2];
+    const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float send = h16 ? a[i] : a[i + 4];
+        const float keep = h16 ? a[i + 4] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float send = h8 ? b[i] : b[i + 2];
+        const float keep = h8 ? b[i + 2] : b[i];
+        c[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const float send = h4 ? c[0] : c[1];
+    const float keep = h4 ? c[1] : c[0];
+    float d = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    d += __shfl_xor_sync(0xffffffffu, d, 2);
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    return d;
+}
+__device__ __forceinline__ int reduce8_row(int lane) {
+    return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+}
+
+// sum over the consumer threads; result broadcast to all of them
+__device__ __forceinline__ float block_sum(float v, float* red, int tid) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    consumer_sync(NCTHR);  // red[] free
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    consumer_sync(NCTHR);
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCWARP; ++i) t += red[i];
+    return t;
+}
+
+// rotate-half RoPE on element d (< D) of a head vector held in global scratch
+__device__ __forceinline__ float rope_elem(const float* vec, int d, int R, const float* cosr, const float* sinr) {
+    const float v = ld_cg_f32(vec + d);
+    if (d >= R) return v;
+    const int half_r = R >> 1;
+    const float c = __ldg(cosr + d), s = __ldg(sinr + d);
+    const float partner = (d < half_r) ? -ld_cg_f32(vec + d + half_r) : ld_cg_f32(vec + d - half_r);
+    return v * c + partner * s;
+}
+
+// ---------------------------------------------------------------- grid barrier
+// All consumer threads call it.  Thread 0 publishes this CTA's writes, counts in,
+// and spins (bounded) until every CTA of the grid has counted in.
+__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned& epoch, unsigned G, int tid,
+                                             const AbortCtl& ab) {
+    consumer_sync(NCTHR);
+    epoch += 1;
+    if (tid == 0) {
+        const unsigned target = epoch * G;
+        __threadfence();
+        atomicAdd(counter, 1u);
+        wait_bounded([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
+        __threadfence();
+    }
+    consumer_sync(NCTHR);
+}
+
+// LayerNorm of x[H] into xbuf (fp32).  which = 0: input norm, 1: post-attention
+// norm.  mean/rstd are computed once per layer (two-pass, fp32) and kept in red[32..33].
+__device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half* gamma, const __half* beta, int H,
+                                                   float* xbuf, float* red, int tid, bool have_stats) {
+    float xv[MAX_H / (NCTHR * 8)][8];
+    const int nvec = H >> 3;
+#pragma unroll
+    for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            const uint4 raw = ld_cg_u32x4(x + v * 8);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(h2[k]);
+                xv[j][2 * k] = f.x;
+                xv[j][2 * k + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) xv[j][k] = 0.f;
+        }
+    }
+    float mean, rstd;
+    if (!have_stats) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_H / (NCTHR * 8); ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) s += xv[j][k];
+        mean = block_sum(s, red, tid) / static_cast<float>(H);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
+            const int v = j * NCTHR + tid;
+            if (v < nvec) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float d = xv[j][k] - mean;
+                    ss = fmaf(d, d, ss);
+                }
+            }
+        }
+        const float var = block_sum(ss, red, tid) / static_cast<float>(H);
+        rstd = rsqrtf(var + 1e-5f);
+        if (tid == 0) {
+            red[32] = mean;
+            red[33] = rstd;
+        }
+    } else {
+        mean = red[32];
+        rstd = red[33];
+    }
+#pragma unroll
+    for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gamma + v * 8));
+            const uint4 braw = __ldg(reinterpret_cast<const uint4*>(beta + v * 8));
+            const __half2* g2 = reinterpret_cast<const __half2*>(&graw);
+            const __half2* b2 = reinterpret_cast<const __half2*>(&braw);
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 g = __half22float2(g2[k]);
+                const float2 b = __half22float2(b2[k]);
+                o[2 * k] = (xv[j][2 * k] - mean) * rstd * g.x + b.x;
+                o[2 * k + 1] = (xv[j][2 * k + 1] - mean) * rstd * g.y + b.y;
+            }
+            *reinterpret_cast<float4*>(xbuf + v * 8) = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(xbuf + v * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+        }
+    }
+    consumer_sync(NCTHR);
+}
+
+// ---------------------------------------------------------------- producer side
+struct Producer {
+    uint32_t ring_addr, full_addr, empty_addr;
+    Cursor cur;
+    uint64_t policy;
+    AbortCtl ab;
+    uint32_t issued;  // stages issued so far
+
+    __device__ __forceinline__ void acquire() {
+        mbar_wait(empty_addr + cur.stage * 8, cur.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
+    }
+    // one stage of `n` row granules (rows g*8.., one box each) at K offset kx
+    __device__ __forceinline__ void rows_stage(const CUtensorMap* tm, int kx, int g0, int n) {
+        acquire();
+        if (*ab.flag) return;
+        const uint32_t bar = full_addr + cur.stage * 8;
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
+        const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
+        for (int w = 0; w < n; ++w) tma_load_2d(dst + w * SLOT_BYTES, tm, kx, (g0 + w) * GRAN, bar, policy);
+        cur.advance();
+        ++issued;
+    }
+    // all stages of a row-partitioned GEMV: granules [g0, g0+cnt) of `tm`, KC chunks each
+    __device__ __forceinline__ void rows_phase(const CUtensorMap* tm, int g0, int cnt, int KC) {
+        if (cnt <= 0) return;
+        const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
+        int g = g0;
+        for (int r = 0; r < nr; ++r) {
+            const int n = base + (r < extra ? 1 : 0);
+            for (int c = 0; c < KC; ++c) rows_stage(tm, c * KCHUNK, g, n);
+            g += n;
+        }
+    }
+    template <int D>
+    __device__ __forceinline__ void kv_stage(const CUtensorMap* tmk, const CUtensorMap* tmv, int h, int ch) {
+        acquire();
+        if (*ab.flag) return;
+        const uint32_t bar = full_addr + cur.stage * 8;
+        constexpr uint32_t TILE = KV_TILE * D * 2;
+        mbar_arrive_expect_tx(bar, 2 * TILE);
+        const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
+        tma_load_2d(dst, tmk, h * D, ch * KV_TILE, bar, policy);
+        tma_load_2d(dst + TILE, tmv, h * D, ch * KV_TILE, bar, policy);
+        cur.advance();
+        ++issued;
+    }
+};
+
+// ---------------------------------------------------------------- consumer side
+struct Consumer {
+    const uint8_t* ring;
+    uint32_t full_addr, empty_addr;
+    Cursor cur;
+    AbortCtl ab;
+    int warp, lane;
+
+    __device__ __forceinline__ const uint8_t* wait_stage() {
+        mbar_wait(full_addr + cur.stage * 8, cur.phase, ab, ST_TIMEOUT_FULL);
+        return ring + static_cast<size_t>(cur.stage) * STAGE_BYTES;
+    }
+    __device__ __forceinline__ void release_stage() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_addr + cur.stage * 8);
+        cur.advance();
+    }
+    // Mirror of Producer::rows_phase.  xs = activations in shared memory (KC*256
+    // floats); epi(granule index relative to g0=0, row in granule, dot product).
+    template <class Epi>
+    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi) {
+        if (cnt <= 0) return;
+        const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
+        int g = 0;
+        for (int r = 0; r < nr; ++r) {
+            const int n = base + (r < extra ? 1 : 0);
+            const bool a0 = warp < n, a1 = warp + NCWARP < n;
+            float acc0[GRAN], acc1[GRAN];
+#pragma unroll
+            for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
+            for (int c = 0; c < KC; ++c) {
+                const uint8_t* st = wait_stage();
+                if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
+                if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, xs + c * KCHUNK, lane, acc1);
+                release_stage();
+            }
+            if (a0) {
+                const float v = warp_reduce8(acc0, lane);
+                if ((lane & 3) == 0) epi(g + warp, reduce8_row(lane), v);
+            }
+            if (a1) {
+                const float v = warp_reduce8(acc1, lane);
+                if ((lane & 3) == 0) epi(g + warp + NCWARP, reduce8_row(lane), v);
+            }
+            g += n;
+        }
+    }
+};
+
+// ---------------------------------------------------------------- the kernel
+template <int D, int CS>
+__global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_constant__ Params p) {
+    static_assert(D % 8 == 0 && D <= 128, "head_dim must be a multiple of 8, at most 128");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const Smem sm = carve(smem_raw, p.nstage, p.xbuf_floats);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const AbortCtl ab{sm.abort_flag, p.status};
+
+    if (tid == 0) {
+        *sm.abort_flag = 0;
+        for (int s = 0; s < p.nstage; ++s) {
+            mbar_init(smem_u32(sm.full + s), 1);
+            mbar_init(smem_u32(sm.empty + s), NCWARP);
+        }
+        mbar_init(smem_u32(sm.xbar), CS > 1 ? CS - 1 : 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if constexpr (CS > 1) dsm::cluster_sync_all();  // peers' barriers exist before any remote arrive
+
+    const int seq = p.seq_ptr ? __ldcg(p.seq_ptr) : p.seq_host;
+    const int H = p.H, NH = p.NH, R = p.R, F = p.F;
+    const int KVW = NH * D;  // cache row width held by this rank
+    {
+        // all CTAs see the same seq, so they all leave together
+        int kv_rows_min = 0x7fffffff;
+        if (p.phase_mask & PH_P2)
+            for (int l = 0; l < p.n_layers; ++l) kv_rows_min = min(kv_rows_min, p.layers[l].kv_rows);
+        if (seq < 0 || ((p.phase_mask & PH_P2) && seq >= kv_rows_min)) {
+            if (tid == 0) atomicCAS(p.status, 0, ST_BAD_SEQ);
+            return;
+        }
+    }
+
+    // ---- static work split (identical on producer and consumer side)
+    const int KC1 = ceil_div(H, KCHUNK);
+    const int NGq = (3 * KVW) / GRAN, NGu = F / GRAN, NG1 = NGq + NGu;
+    const int g1a = part_begin(cta, NG1, G), g1b = part_begin(cta + 1, NG1, G);
+    const int qa = min(g1a, NGq), qb = min(g1b, NGq);              // QKV granules [qa, qb)
+    const int ua = max(g1a, NGq) - NGq, ub = max(g1b, NGq) - NGq;  // up granules [ua, ub)
+    const int nch = ceil_div(seq, KV_TILE);
+    const int T2 = NH * nch;
+    const int t2a = part_begin(cta, T2, G), t2b = part_begin(cta + 1, T2, G);
+    const int NC = G / CS, cl = cta / CS;
+    const int me = (CS > 1) ? static_cast<int>(dsm::cta_rank()) : 0;
+    const int NG3 = H / GRAN;
+    const int g3a = part_begin(cl, NG3, NC), g3b = part_begin(cl + 1, NG3, NC);
+    const int KCo = (p.p3_flags & F3_USE_O) ? ceil_div(KVW, KCHUNK) : 0;
+    const int KCd = (p.p3_flags & F3_USE_DOWN) ? ceil_div(F, KCHUNK) : 0;
+    const int KC3 = KCo + KCd;
+    const int my3 = (KC3 > me) ? ceil_div(KC3 - me, CS) : 0;  // chunks me, me+CS, ...
+    int NG4 = 0, g4a = 0, g4b = 0;
+    if (p.phase_mask & PH_P4) {
+        NG4 = ceil_div(p.tail->vocab, GRAN);
+        g4a = part_begin(cta, NG4, G);
+        g4b = part_begin(cta + 1, NG4, G);
+    }
+
+    // =========================================================== producer warp
+    if (warp == NCWARP) {
+        if (lane == 0) {
+            Producer pr;
+            pr.ring_addr = smem_u32(sm.ring);
+            pr.full_addr = smem_u32(sm.full);
+            pr.empty_addr = smem_u32(sm.empty);
+            pr.cur = Cursor{0, 0u, p.nstage};
+            pr.policy = l2_policy_evict_first();
+            pr.ab = ab;
+            pr.issued = 0;
+            for (int l = 0; l < p.n_layers; ++l) {
+                const LayerDesc* L = p.layers + l;
+                if (p.phase_mask & PH_P1) {
+                    pr.rows_phase(&L->tm_qkv, qa, qb - qa, KC1);
+                    pr.rows_phase(&L->tm_up, ua, ub - ua, KC1);
+                }
+                if (p.phase_mask & PH_P2) {
+                    for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(&L->tm_k, &L->tm_v, t / nch, t % nch);
+                }
+                if (p.phase_mask & PH_P3) {
+                    const int cnt = g3b - g3a;
+                    if (cnt > 0 && my3 > 0) {
+                        const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
+                        int g = g3a;
+                        for (int r = 0; r < nr; ++r) {
+                            const int n = base + (r < extra ? 1 : 0);
+                            for (int i = 0; i < my3; ++i) {
+                                const int q = me + i * CS;
+                                if (q < KCo) pr.rows_stage(&L->tm_o, q * KCHUNK, g, n);
+                                else pr.rows_stage(&L->tm_down, (q - KCo) * KCHUNK, g, n);
+                            }
+                            g += n;
+                        }
+                    }
+                }
+            }
+            if (p.phase_mask & PH_P4) pr.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
+            // After an abort the consumers stop draining the ring: give the copies
+            // already issued a bounded chance to land before this CTA's shared
+            // memory goes away.
+            if (*ab.flag) {
+                const unsigned long long t0 = globaltimer_ns();
+                const uint32_t back = min(pr.issued, static_cast<uint32_t>(p.nstage));
+                Cursor c = pr.cur;
+                for (uint32_t k = 0; k < back; ++k) {
+                    // step the cursor back one stage
+                    if (c.stage == 0) { c.stage = c.nstage - 1; c.phase ^= 1u; } else { --c.stage; }
+                    const uint32_t bar = pr.full_addr + c.stage * 8;
+                    while (!mbar_try_wait(bar, c.phase)) {
+                        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                            atomicCAS(p.status, ST_OK, ST_TIMEOUT_DRAIN);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ======================================================= consumer warps
+        Consumer co;
+        co.ring = sm.ring;
+        co.full_addr = smem_u32(sm.full);
+        co.empty_addr = smem_u32(sm.empty);
+        co.cur = Cursor{0, 0u, p.nstage};
+        co.ab = ab;
+        co.warp = warp;
+        co.lane = lane;
+        unsigned epoch = 0;
+        uint32_t xparity = 0;
+        const int pos_off = p.rope_stride * seq;
+        const float* cosr = p.cos + pos_off;
+        const float* sinr = p.sin + pos_off;
+        const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
+        bool need_barrier = false;  // a phase of this launch wrote data the next one reads
+
+        const __half* x_first = p.embed ? (p.embed + static_cast<size_t>(__ldcg(p.token_in)) * H) : p.x_in;
+
+        for (int l = 0; l < p.n_layers; ++l) {
+            const LayerDesc* L = p.layers + l;
+            const __half* x = (l == 0) ? x_first : p.hid[(l - 1) & 1];
+            __half* y = (l == p.n_layers - 1) ? p.out : p.hid[l & 1];
+
+            // ------------------------------------------------------------ P1
+            if (p.phase_mask & PH_P1) {
+                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                bool have_stats = false;
+                if (qb > qa) {
+                    layer_norm_to_smem(x, L->ln_w, L->ln_b, H, sm.xbuf, sm.red, tid, have_stats);
+                    have_stats = true;
+                    const __half* bq = L->b_qkv;
+                    float* dst = p.qkv_f32;
+                    const int row0 = qa * GRAN;
+                    co.rows_phase(qb - qa, KC1, sm.xbuf, [&](int g, int r, float v) {
+                        const int row = row0 + g * GRAN + r;
+                        dst[row] = v + __half2float(__ldg(bq + row));
+                    });
+                    consumer_sync(NCTHR);  // xbuf is rewritten next
+                }
+                if (ub > ua) {
+                    layer_norm_to_smem(x, L->pln_w, L->pln_b, H, sm.xbuf, sm.red, tid, have_stats);
+                    const __half* bu = L->b_up;
+                    float* dst = p.mid_f32;
+                    __half* dst16 = p.mid_f16_out;
+                    const int row0 = ua * GRAN;
+                    co.rows_phase(ub - ua, KC1, sm.xbuf, [&](int g, int r, float v) {
+                        const int row = row0 + g * GRAN + r;
+                        const float a = gelu_tanh_f(v + __half2float(__ldg(bu + row)));
+                        dst[row] = a;
+                        if (dst16) dst16[row] = __float2half_rn(a);
+                    });
+                }
+                need_barrier = true;
+            }
+
+            // ------------------------------------------------------------ P2
+            if (p.phase_mask & PH_P2) {
+                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                // new token: RoPE, cache append, and its own softmax partial
+                if (warp == 0) {
+                    for (int h = 0; h < NH; ++h) {
+                        if (head_owner(h, NH, G) != cta) continue;
+                        const float* qv = p.qkv_f32 + h * 3 * D;
+                        float s = 0.f;
+                        for (int d = lane; d < D; d += 32) {
+                            const float qd = rope_elem(qv, d, R, cosr, sinr) * qscale;
+                            const __half k16 = __float2half_rn(rope_elem(qv + D, d, R, cosr, sinr));
+                            const __half v16 = __float2half_rn(ld_cg_f32(qv + 2 * D + d));
+                            s = fmaf(qd, __half2float(k16), s);
+                            const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
+                            L->k_cache[off] = k16;
+                            L->v_cache[off] = v16;
+                            if (p.k_new) p.k_new[h * D + d] = k16;
+                            if (p.v_new) p.v_new[h * D + d] = v16;
+                            p.attn_new[h * (D + 2) + d] = __half2float(v16);
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                        if (lane == 0) {
+                            p.attn_new[h * (D + 2) + D] = s;
+                            p.attn_new[h * (D + 2) + D + 1] = 1.0f;
+                        }
+                    }
+                }
+                // cached rows: items [t2a, t2b), head-major
+                const int hw = lane >> 4, l16 = lane & 15;
+                const bool dim_ok = l16 * 8 < D;
+                float* mbuf = sm.xbuf;                 // [16][D]
+                float* mlbuf = sm.xbuf + 16 * D;       // [16][2]
+                int cur_h = -1;
+                float qreg[8], acc[8], m_run = -INFINITY, l_run = 0.f;
+                const int h_first = (t2b > t2a) ? t2a / nch : 0;
+
+                auto flush = [&](int h) {
+                    const int slot = warp * 2 + hw;
+                    if (dim_ok) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) mbuf[slot * D + l16 * 8 + k] = acc[k];
+                    }
+                    if (l16 == 0) {
+                        mlbuf[slot * 2] = m_run;
+                        mlbuf[slot * 2 + 1] = l_run;
+                    }
+                    consumer_sync(NCTHR);
+                    float* dst = p.attn_part + (static_cast<size_t>(cta) * MAXL + (h - h_first)) * (D + 2);
+                    if (tid < D) {
+                        float M = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) M = fmaxf(M, mlbuf[i * 2]);
+                        float a = 0.f, lsum = 0.f;
+                        if (M > -INFINITY) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float w = exp2f(mlbuf[i * 2] - M);
+                                a = fmaf(mbuf[i * D + tid], w, a);
+                                lsum = fmaf(mlbuf[i * 2 + 1], w, lsum);
+                            }
+                        }
+                        dst[tid] = a;
+                        if (tid == 0) {
+                            dst[D] = M;
+                            dst[D + 1] = lsum;
+                        }
+                    }
+                    consumer_sync(NCTHR);
+                };
+
+                for (int t = t2a; t < t2b; ++t) {
+                    const int h = t / nch, ch = t - h * nch;
+                    if (h != cur_h) {
+                        if (cur_h >= 0) flush(cur_h);
+                        cur_h = h;
+                        if (tid < D) sm.q_s[tid] = rope_elem(p.qkv_f32 + h * 3 * D, tid, R, cosr, sinr) * qscale;
+                        consumer_sync(NCTHR);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            qreg[k] = dim_ok ? sm.q_s[l16 * 8 + k] : 0.f;
+                            acc[k] = 0.f;
+                        }
+                        m_run = -INFINITY;
+                        l_run = 0.f;
+                    }
+                    const uint8_t* st = co.wait_stage();
+                    const __half* kt = reinterpret_cast<const __half*>(st);
+                    const __half* vt = kt + KV_TILE * D;
+                    const int r0 = warp * 8 + hw * 4;
+                    float s[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float d = 0.f;
+                        if (dim_ok) {
+                            const uint4 raw = *reinterpret_cast<const uint4*>(kt + (r0 + j) * D + l16 * 8);
+                            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float2 f = __half22float2(h2[k]);
+                                d = fmaf(f.x, qreg[2 * k], d);
+                                d = fmaf(f.y, qreg[2 * k + 1], d);
+                            }
+                        }
+                        s[j] = d;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+                    }
+                    const int grow = ch * KV_TILE + r0;
+                    float mx = m_run;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (grow + j >= seq) s[j] = -INFINITY;
+                        mx = fmaxf(mx, s[j]);
+                    }
+                    if (mx > -INFINITY) {
+                        const float sc = exp2f(m_run - mx);
+                        l_run *= sc;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[k] *= sc;
+                        m_run = mx;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (grow + j < seq) {
+                                const float pj = exp2f(s[j] - mx);
+                                l_run += pj;
+                                if (dim_ok) {
+                                    const uint4 raw = *reinterpret_cast<const uint4*>(vt + (r0 + j) * D + l16 * 8);
+                                    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                                    for (int k = 0; k < 4; ++k) {
+                                        const float2 f = __half22float2(h2[k]);
+                                        acc[2 * k] = fmaf(pj, f.x, acc[2 * k]);
+                                        acc[2 * k + 1] = fmaf(pj, f.y, acc[2 * k + 1]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    co.release_stage();
+                }
+                if (cur_h >= 0) flush(cur_h);
+                need_barrier = true;
+            }
+
+            // ------------------------------------------------------------ P3
+            if (p.phase_mask & PH_P3) {
+                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                // this CTA's K slice of [attn ; mid] as fp32 in xbuf, chunk-major
+                for (int i = 0; i < my3; ++i) {
+                    const int q = me + i * CS;
+                    float val = 0.f;
+                    if (q < KCo) {
+                        const int e = q * KCHUNK + tid;
+                        if (e < KVW) {
+                            const int h = e / D, d = e - h * D;
+                            const float* pn = p.attn_new + h * (D + 2);
+                            float M = ld_cg_f32(pn + D);
+                            int ia = 0, ib = -1;
+                            if (nch > 0) {
+                                ia = part_of(h * nch, T2, G);
+                                ib = part_of((h + 1) * nch - 1, T2, G);
+                            }
+                            // CTAs strictly between ia and ib may own no item at all (T2 < G)
+                            for (int c = ia; c <= ib; ++c) {
+                                const int b0 = part_begin(c, T2, G);
+                                if (part_begin(c + 1, T2, G) == b0) continue;
+                                const int loc = h - b0 / nch;
+                                M = fmaxf(M, ld_cg_f32(p.attn_part + (static_cast<size_t>(c) * MAXL + loc) * (D + 2) + D));
+                            }
+                            float w = exp2f(ld_cg_f32(pn + D) - M);
+                            float den = w * ld_cg_f32(pn + D + 1);
+                            float num = w * ld_cg_f32(pn + d);
+                            for (int c = ia; c <= ib; ++c) {
+                                const int b0 = part_begin(c, T2, G);
+                                if (part_begin(c + 1, T2, G) == b0) continue;
+                                const int loc = h - b0 / nch;
+                                const float* pp = p.attn_part + (static_cast<size_t>(c) * MAXL + loc) * (D + 2);
+                                w = exp2f(ld_cg_f32(pp + D) - M);
+                                den = fmaf(w, ld_cg_f32(pp + D + 1), den);
+                                num = fmaf(w, ld_cg_f32(pp + d), num);
+                            }
+                            val = num / den;
+                        }
+                    } else {
+                        const int e = (q - KCo) * KCHUNK + tid;
+                        if (e < F) {
+                            val = (p.p3_flags & F3_MID_F16) ? __half2float(ld_cg_f16(p.mid_f16_in + e))
+                                                            : ld_cg_f32(p.mid_f32 + e);
+                        }
+                    }
+                    sm.xbuf[i * KCHUNK + tid] = val;
+                }
+                consumer_sync(NCTHR);
+
+                const int cnt = g3b - g3a;
+                const int nrows = cnt * GRAN;
+                if (cnt > 0) {
+                    if (my3 > 0) {
+                        float* ps = sm.part_s;
+                        co.rows_phase(cnt, my3, sm.xbuf, [&](int g, int r, float v) { ps[g * GRAN + r] = v; });
+                    } else {
+                        for (int t = tid; t < nrows; t += NCTHR) sm.part_s[t] = 0.f;
+                    }
+                }
+                const int stride = MAX_P3_ROWS / CS;
+                dsm::reduce_scatter_push<CS>(sm.part_s, sm.recv, stride, nrows, sm.xbar, xparity, tid, NCTHR, ab);
+                xparity ^= 1u;
+                for (int j = tid; me + j * CS < nrows; j += NCTHR) {
+                    const int row = g3a * GRAN + me + j * CS;
+                    float v = dsm::tree_sum<CS>(sm.recv, stride, j);
+                    if (p.p3_flags & F3_ADD_BO) v += __half2float(__ldg(L->b_o + row));
+                    if (p.p3_flags & F3_ADD_BDOWN) v += __half2float(__ldg(L->b_down + row));
+                    if (p.p3_flags & F3_ADD_X) v += __half2float(ld_cg_f16(x + row));
+                    if (p.extra_add_f16) v += __half2float(ld_cg_f16(p.extra_add_f16 + row));
+                    y[row] = __float2half_rn(v);
+                }
+                need_barrier = true;
+            }
+        }
+
+        // ---------------------------------------------------------------- P4
+        if (p.phase_mask & PH_P4) {
+            const TailDesc* Tl = p.tail;
+            const __half* x = (p.n_layers > 0) ? p.out : x_first;
+            if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+            float best = -INFINITY;
+            int best_i = 0x7fffffff;
+            if (g4b > g4a) {
+                layer_norm_to_smem(x, Tl->fln_w, Tl->fln_b, H, sm.xbuf, sm.red, tid, false);
+                const int row0 = g4a * GRAN, V = Tl->vocab;
+                float* lg = p.logits;
+                co.rows_phase(g4b - g4a, KC1, sm.xbuf, [&](int g, int r, float v) {
+                    const int row = row0 + g * GRAN + r;
+                    if (row < V) {
+                        if (lg) lg[row] = v;
+                        if (v > best || (v == best && row < best_i)) {
+                            best = v;
+                            best_i = row;
+                        }
+                    }
+                });
+            }
+            // arg-max: warp, then CTA, then (after a grid barrier) CTA 0
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+                if (ov > best || (ov == best && oi < best_i)) {
+                    best = ov;
+                    best_i = oi;
+                }
+            }
+            consumer_sync(NCTHR);
+            int* redi = reinterpret_cast<int*>(sm.red + 16);
+            if (lane == 0) {
+                sm.red[warp] = best;
+                redi[warp] = best_i;
+            }
+            consumer_sync(NCTHR);
+            if (tid == 0) {
+                for (int i = 1; i < NCWARP; ++i) {
+                    if (sm.red[i] > best || (sm.red[i] == best && redi[i] < best_i)) {
+                        best = sm.red[i];
+                        best_i = redi[i];
+                    }
+                }
+                p.amax_val[cta] = best;
+                p.amax_idx[cta] = best_i;
+            }
+            grid_barrier(p.sync, epoch, G, tid, ab);
+            if (cta == 0 && warp == 0) {
+                float b = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int i = lane; i < G; i += 32) {
+                    const float v = __ldcg(p.amax_val + i);
+                    const int vi = __ldcg(p.amax_idx + i);
+                    if (v > b || (v == b && vi < bi)) {
+                        b = v;
+                        bi = vi;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, b, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (ov > b || (ov == b && oi < bi)) {
+                        b = ov;
+                        bi = oi;
+                    }
+                }
+                if (lane == 0) {
+                    if (p.token_out) *p.token_out = bi + p.vocab_offset;
+                    p.amax_val[0] = b;  // winner's logit, for vocabulary-sharded callers
+                    p.amax_idx[0] = bi + p.vocab_offset;
+                }
+            }
+        }
+
+        // ---- leave: count out; the last CTA re-arms the barrier words
+        if (epoch > 0 || p.seq_inc) {
+            consumer_sync(NCTHR);
+            if (tid == 0) {
+                __threadfence();
+                const unsigned old = atomicAdd(p.sync + 1, 1u);
+                if (old == static_cast<unsigned>(G) - 1u) {
+                    p.sync[0] = 0u;
+                    p.sync[1] = 0u;
+                    if (p.seq_inc) *p.seq_inc = seq + 1;
+                    __threadfence();
+                }
+            }
+        }
+    }
+    // no CTA leaves while a peer may still store into its shared memory
+    __syncthreads();
+    if constexpr (CS > 1) dsm::cluster_sync_all();
+}
+
+}  // namespace cfb

@@ -1,0 +1,162 @@
+"""Whole-model greedy decode on one GPU: the decode loop the reference drives from
+Python (tests/benchmark_decode_6b9.py:133-198: embed_in -> 32 layer ops ->
+final LayerNorm -> embed_out -> argmax -> .item()) as ONE persistent launch per
+token, optionally captured in a CUDA graph.  Token id and sequence length live
+in device memory, so the same graph replays for every token.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import CfDecoderConfig, CfDims, CfHeadWeights, CfLayerWeights, check, lib
+from .api import _req, _wrap
+
+_LAYER_KEYS = {
+    "qkv_weight": "qkv_weight", "qkv_bias": "qkv_bias", "o_weight": "o_weight", "o_bias": "o_bias",
+    "ln_weight": "ln_weight", "ln_bias": "ln_bias", "post_ln_weight": "post_ln_weight",
+    "post_ln_bias": "post_ln_bias", "mlp_up_weight": "mlp_up_weight", "mlp_up_bias": "mlp_up_bias",
+    "mlp_down_weight": "mlp_down_weight", "mlp_down_bias": "mlp_down_bias",
+}
+
+
+def rope_table(max_pos: int, rotary: int, device, base: float = 10000.0):
+    """[max_pos, rotary] fp32 cos/sin with emb = cat(freqs, freqs)
+    (precompute_rope_embeddings, tests/benchmark_decode_6b9.py:23-34 of the reference)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, rotary, 2, dtype=torch.float32, device=device) / rotary))
+    pos = torch.arange(0, max_pos, dtype=torch.float32, device=device)
+    freqs = torch.outer(pos, inv_freq)
+    emb = torch.cat([freqs, freqs], dim=-1)
+    return emb.cos().contiguous(), emb.sin().contiguous()
+
+
+def layer_weights_struct(d: CfDims, w: Dict[str, torch.Tensor]) -> CfLayerWeights:
+    H, KVW, F = d.hidden, d.heads * d.head_dim, d.ffn
+    sizes = {"qkv_weight": 3 * KVW * H, "qkv_bias": 3 * KVW, "o_weight": H * KVW, "o_bias": H, "ln_weight": H,
+             "ln_bias": H, "post_ln_weight": H, "post_ln_bias": H, "mlp_up_weight": F * H, "mlp_up_bias": F,
+             "mlp_down_weight": H * F, "mlp_down_bias": H}
+    s = CfLayerWeights()
+    for field, key in _LAYER_KEYS.items():
+        setattr(s, field, _req(w[key], key, sizes[field]))
+    return s
+
+
+class PythiaDecoder:
+    """Greedy decoder over caller-owned fp16 weights and KV caches.
+
+    layers : list of dicts with the 12 tensors of a layer (keys as in CfLayerWeights)
+    head   : dict with embed_in [V,H], final_ln_weight, final_ln_bias, embed_out [V,H]
+    caches : list of (k_cache, v_cache), each [max_seq, heads*head_dim] fp16
+    """
+
+    def __init__(self, dims: CfDims, layers: Sequence[Dict[str, torch.Tensor]], head: Dict[str, torch.Tensor],
+                 caches: Sequence, max_seq: int, use_graph: bool = True):
+        self.dims, self.layers, self.head, self.caches = dims, list(layers), head, list(caches)
+        self.max_seq = int(max_seq)
+        self.device = head["embed_in"].device
+        self.cos, self.sin = rope_table(self.max_seq, dims.rotary, self.device)
+        cfg = CfDecoderConfig()
+        cfg.dims = dims
+        cfg.n_layers = len(self.layers)
+        cfg.max_seq_len = self.max_seq
+        cfg.tp_size, cfg.tp_rank = 1, 0
+        cfg.cos_table, cfg.sin_table = self.cos.data_ptr(), self.sin.data_ptr()
+        h = C.c_int64(0)
+        check(lib.cf_decoder_create(C.byref(cfg), C.byref(h)))
+        self.handle = h.value
+        KVW = dims.heads * dims.head_dim
+        for i, (w, (k, v)) in enumerate(zip(self.layers, self.caches)):
+            if k.shape != (self.max_seq, KVW) or v.shape != (self.max_seq, KVW):
+                raise RuntimeError(f"layer {i}: caches must be [{self.max_seq}, {KVW}]")
+            check(lib.cf_decoder_set_layer(self.handle, i, C.byref(layer_weights_struct(dims, w)),
+                                           _req(k, "k_cache", k.numel()), _req(v, "v_cache", v.numel())))
+        hw = CfHeadWeights()
+        hw.embed_in = _req(head["embed_in"], "embed_in", head["embed_in"].numel())
+        hw.final_ln_weight = _req(head["final_ln_weight"], "final_ln_weight", dims.hidden)
+        hw.final_ln_bias = _req(head["final_ln_bias"], "final_ln_bias", dims.hidden)
+        hw.embed_out = _req(head["embed_out"], "embed_out", dims.vocab * dims.hidden)
+        hw.vocab_offset = 0
+        check(lib.cf_decoder_set_head(self.handle, C.byref(hw)))
+        check(lib.cf_decoder_finalize(self.handle))
+        p = [C.c_void_p() for _ in range(7)]
+        check(lib.cf_decoder_state(self.handle, *[C.byref(x) for x in p]))
+        dev = self.device
+        self.token = torch.as_tensor(_IntView(p[0].value, (1,)), device=dev)
+        self.seq_len = torch.as_tensor(_IntView(p[1].value, (1,)), device=dev)
+        self.logits = torch.as_tensor(_F32View(p[2].value, (dims.vocab,)), device=dev)
+        self.hidden = _wrap(p[3].value, (1, dims.hidden), dev)
+        self.use_graph = use_graph
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def reset(self, seq_len: int, token: int) -> None:
+        """Position the decoder: `seq_len` rows of every cache are valid, `token` is fed next."""
+        self.seq_len.fill_(int(seq_len))
+        self.token.fill_(int(token))
+
+    def _enqueue(self) -> None:
+        check(lib.cf_decoder_step(self.handle, torch.cuda.current_stream().cuda_stream))
+
+    def capture(self) -> None:
+        """Record one token step into a CUDA graph (state words are restored afterwards)."""
+        seq0, tok0 = self.seq_len.clone(), self.token.clone()
+        # warm-up launch on a side stream, as torch's capture rules want
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._enqueue()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._enqueue()
+        self._graph = g
+        # the warm-up wrote one cache row at seq0 and advanced the state: rewind
+        self.seq_len.copy_(seq0)
+        self.token.copy_(tok0)
+
+    def step(self) -> None:
+        """Decode one token: consumes self.token at position self.seq_len, leaves the
+        arg-max token in self.token and seq_len + 1 in self.seq_len.  Asynchronous."""
+        if self.use_graph:
+            if self._graph is None:
+                self.capture()
+            self._graph.replay()
+        else:
+            self._enqueue()
+
+    def generate(self, first_token: int, seq_len: int, n_tokens: int) -> List[int]:
+        """Greedy rollout; returns the n_tokens generated ids (one host read per token,
+        like the reference loop's .item())."""
+        self.reset(seq_len, first_token)
+        out = []
+        for _ in range(n_tokens):
+            self.step()
+            out.append(int(self.token.item()))
+        return out
+
+    def close(self) -> None:
+        if self.handle:
+            self._graph = None
+            check(lib.cf_decoder_destroy(self.handle))
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class _IntView:
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<i4", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class _F32View:
+    def __init__(self, ptr, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (ptr, False),
+                                         "version": 3, "strides": None}

@@ -1,0 +1,207 @@
+/* clusterfusion_b200.h — C ABI of the B200 (sm_100a) fused Pythia/GPT-NeoX decode path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes, and
+ * returns 0 on success or a negative CF_ERR_* code; cf_last_error() then gives a
+ * thread-local message.  All tensors are contiguous fp16 on the current CUDA
+ * device unless stated otherwise; cos/sin are fp32.  `stream` is a cudaStream_t
+ * passed as void* (NULL = legacy default stream).  Nothing here synchronises the
+ * device unless its comment says so.
+ *
+ * Each declaration cites the interface of the reference project
+ * (superk668/ClusterFusionPlus) that it replaces, as file:line.
+ */
+#ifndef CLUSTERFUSION_B200_H_
+#define CLUSTERFUSION_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CF_OK 0
+#define CF_ERR_INVALID (-1)   /* bad argument (shape, alignment, range, unknown id) */
+#define CF_ERR_CUDA (-2)      /* a CUDA runtime / driver call failed */
+#define CF_ERR_DEVICE (-3)    /* the kernel reported a device-side status (timeout, bad seq_len) */
+#define CF_ERR_UNSUPPORTED (-4)
+
+/* Model ids of the reference's per-model entry points. */
+#define CF_PYTHIA_2B8 0   /* include/5090/pythia_2b8/config.h:6-12  */
+#define CF_PYTHIA_6B9 1   /* include/5090/pythia_6b9/config.h:6-12  */
+
+/* Geometry of (a shard of) a GPT-NeoX style model.  `heads` and `ffn` are what
+ * THIS rank holds; hidden is always the full width. */
+typedef struct CfDims {
+    int hidden;    /* HIDDEN_DIM */
+    int heads;     /* HEAD_NUM (local) */
+    int head_dim;  /* HEAD_DIM: 80 or 128 */
+    int rotary;    /* ROTARY_DIM */
+    int ffn;       /* FFN_DIM (local) */
+    int vocab;     /* LM-head rows held by this rank (0 = no tail) */
+} CfDims;
+
+/* The 12 parameter tensors of one layer; argument order of
+ * include/pybind.cpp:109-129 (pythia_*_decoder_layer_sm120). */
+typedef struct CfLayerWeights {
+    const void* qkv_weight;      /* [3*heads*head_dim, hidden], rows interleaved per head [Q_h;K_h;V_h] */
+    const void* qkv_bias;        /* [3*heads*head_dim] */
+    const void* o_weight;        /* [hidden, heads*head_dim] */
+    const void* o_bias;          /* [hidden] */
+    const void* ln_weight;       /* [hidden] */
+    const void* ln_bias;
+    const void* post_ln_weight;  /* [hidden] */
+    const void* post_ln_bias;
+    const void* mlp_up_weight;   /* [ffn, hidden] */
+    const void* mlp_up_bias;     /* [ffn] */
+    const void* mlp_down_weight; /* [hidden, ffn] */
+    const void* mlp_down_bias;   /* [hidden] */
+} CfLayerWeights;
+
+/* Per-call tensors of one layer call. */
+typedef struct CfLayerIO {
+    const void* input;       /* [1, hidden] */
+    void* k_cache;           /* [kv_rows, heads*head_dim]; row seq_len is written */
+    void* v_cache;
+    int64_t kv_rows;         /* rows allocated in each cache; seq_len must be < kv_rows */
+    const float* cos;        /* fp32, first `rotary` entries used */
+    const float* sin;
+    void* output;            /* [1, hidden] */
+    void* k_new;             /* [1, heads, head_dim] or NULL */
+    void* v_new;
+    void* attn_output;       /* attention_only: [1, hidden] */
+    void* mlp_intermediate;  /* attention_only: [ffn] */
+} CfLayerIO;
+
+const char* cf_last_error(void);
+
+/* Geometry of a built-in model id. */
+int cf_model_dims(int model, CfDims* out);
+
+/* Launch geometry the library chose on the current device: SM count, CTAs in the
+ * persistent grid, cluster size, TMA ring stages for `model`. */
+int cf_launch_info(int model, int* sm_count, int* grid, int* cluster, int* stages, int* smem_bytes);
+
+/* Reads the device status word of the current device (synchronises the device),
+ * clears it and re-arms the barrier words if it was set.  *status = 0 when every
+ * launch so far finished normally. */
+int cf_get_status(int* status);
+
+/* Fused decoder layer, one token at batch 1.
+ * Replaces pythia_2b8_decoder_layer_sm120 / pythia_6b9_decoder_layer_sm120
+ * (include/pybind.cpp:109-129,198-218; include/5090/pythia_6b9/pythia_kernel_dispatch.cu:4-236). */
+int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, void* stream);
+
+/* Same result (bit for bit) from two launches with the kernel boundary in place
+ * of the second grid barrier.
+ * Replaces pythia_2b8_decoder_layer_split_sm120 (include/pybind.cpp:132-151;
+ * include/5090/pythia_2b8/pythia_kernel_dispatch_split.cu:18-218). */
+int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
+                                  void* stream);
+
+/* Attention half: io->attn_output = dense(attention) + o_bias, io->mlp_intermediate =
+ * gelu(up(post_ln(x))), io->k_new / io->v_new.  mlp_down_* of `w` may be NULL.
+ * Replaces pythia_2b8_attention_only_sm120 (include/pybind.cpp:154-171;
+ * pythia_kernel_dispatch_split.cu:225-359). */
+int cf_pythia_attention_only(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, void* stream);
+
+/* MLP half: output = input + attn_output + down(mlp_intermediate) + down_bias.
+ * Replaces pythia_2b8_mlp_only_sm120 (include/pybind.cpp:174-180;
+ * pythia_kernel_dispatch_split.cu:364-426). */
+int cf_pythia_mlp_only(int model, const void* input, const void* attn_output, const void* mlp_intermediate,
+                       const void* mlp_down_weight, const void* mlp_down_bias, void* output, void* stream);
+
+/* Persistent per-layer context: tensor maps sized to max_seq_len and static
+ * output buffers owned by the library.
+ * Replaces pythia_*_create_graph_context_sm120 (include/pybind.cpp:206-215;
+ * include/5090/pythia_6b9/pythia_kernel_dispatch_graph.cu:77-206). */
+int cf_pythia_create_graph_context(int model, int64_t context_id, void* k_cache, void* v_cache,
+                                   const void* weight_qkv, const void* weight_o, const void* mlp_up_weight,
+                                   const void* mlp_down_weight, int64_t max_seq_len);
+
+/* Small per-step tensors of graph_decode_step, order of include/pybind.cpp:217-233. */
+typedef struct CfStepArgs {
+    const void* input;
+    const void* ln_weight;
+    const void* ln_bias;
+    const void* qkv_bias;
+    const void* o_bias;
+    const float* cos;
+    const float* sin;
+    void* k_cache;
+    void* v_cache;
+    const void* post_ln_weight;
+    const void* post_ln_bias;
+    const void* mlp_up_bias;
+    const void* mlp_down_bias;
+} CfStepArgs;
+
+/* One layer step through a context.  *output, *k_new, *v_new receive pointers to
+ * the context's static buffers ([hidden], [heads*head_dim] x2), valid until the
+ * context is destroyed and overwritten by the next step.
+ * Replaces pythia_*_graph_decode_step_sm120 (include/pybind.cpp:217-233;
+ * pythia_kernel_dispatch_graph.cu:212-287). */
+int cf_pythia_graph_decode_step(int model, int64_t context_id, const CfStepArgs* a, int64_t seq_len, void* stream,
+                                void** output, void** k_new, void** v_new);
+
+/* Optional: make a context replayable inside a captured CUDA graph.  With a
+ * device-resident sequence length and a RoPE table ([rows, stride] fp32 each) the
+ * step reads both from device memory, so the seq_len / cos / sin arguments of
+ * cf_pythia_graph_decode_step are ignored.  NULL pointers switch back.
+ * (The reference bakes seq_len into the launch: pythia_kernel_dispatch_graph.cu:260-261.) */
+int cf_pythia_graph_set_device_state(int model, int64_t context_id, const int* seq_len_dev, const float* cos_table,
+                                     const float* sin_table, int64_t table_stride);
+
+/* Replaces pythia_*_destroy_graph_context_sm120 (pythia_kernel_dispatch_graph.cu:292-294). */
+int cf_pythia_destroy_graph_context(int model, int64_t context_id);
+
+/* ---------------------------------------------------------------------------
+ * Whole-model greedy decoder: embedding gather -> n_layers fused layers ->
+ * final LayerNorm -> LM head -> argmax, one persistent launch per token,
+ * capture-safe (no allocation, no host sync, sequence length and token id live
+ * in device memory).  The reference runs this loop in Python around its layer
+ * op (tests/benchmark_decode_6b9.py:133-198).
+ * ------------------------------------------------------------------------- */
+typedef struct CfDecoderConfig {
+    CfDims dims;
+    int n_layers;
+    int64_t max_seq_len;     /* rows of every KV cache */
+    int tp_size;             /* 1 = single GPU */
+    int tp_rank;
+    const float* cos_table;  /* [max_seq_len, rotary] fp32 */
+    const float* sin_table;
+} CfDecoderConfig;
+
+typedef struct CfHeadWeights {
+    const void* embed_in;         /* [vocab_total, hidden] */
+    const void* final_ln_weight;  /* [hidden] */
+    const void* final_ln_bias;
+    const void* embed_out;        /* [vocab (local), hidden] */
+    int vocab_offset;             /* first vocabulary row held by this rank */
+} CfHeadWeights;
+
+int cf_decoder_create(const CfDecoderConfig* cfg, int64_t* handle);
+int cf_decoder_set_layer(int64_t handle, int layer, const CfLayerWeights* w, void* k_cache, void* v_cache);
+int cf_decoder_set_head(int64_t handle, const CfHeadWeights* head);
+/* Uploads descriptors; must be called once after the setters, outside capture. */
+int cf_decoder_finalize(int64_t handle);
+/* Device-resident state: token id (in/out), sequence length, logits [vocab] fp32,
+ * last hidden state [hidden] fp16, and (tensor-parallel) the fp16 partial [hidden]
+ * that the caller all-reduces and the (max logit, index) pair of this shard. */
+int cf_decoder_state(int64_t handle, int** token, int** seq_len, float** logits, void** hidden, void** partial,
+                     float** shard_max, int** shard_idx);
+/* Enqueue one whole token on `stream` (tp_size == 1). */
+int cf_decoder_step(int64_t handle, void* stream);
+/* Tensor-parallel pieces, enqueued per layer around the caller's all-reduce of
+ * `partial`: layer_partial -> all-reduce(partial) -> layer_finish; then tail. */
+int cf_decoder_layer_partial(int64_t handle, int layer, void* stream);
+int cf_decoder_layer_finish(int64_t handle, int layer, void* stream);
+int cf_decoder_tail(int64_t handle, void* stream);
+/* After the caller gathered every shard's (max, idx): pick the winner into the
+ * token word and advance seq_len. pairs_val/pairs_idx are device arrays of tp_size. */
+int cf_decoder_select_token(int64_t handle, const float* pairs_val, const int* pairs_idx, void* stream);
+int cf_decoder_destroy(int64_t handle);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLUSTERFUSION_B200_H_ */
