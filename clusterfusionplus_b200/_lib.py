@@ -58,6 +58,7 @@ SIGNATURES = {
     "cf_get_status": (C.c_int, [_P(C.c_int)]),
     "cf_pythia_decoder_layer": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
     "cf_pythia_decoder_layer_split": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
+    "cf_debug_run_phases": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_int, C.c_void_p]),
     "cf_pythia_attention_only": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
     "cf_pythia_mlp_only": (C.c_int, [C.c_int] + [C.c_void_p] * 7),
     "cf_pythia_create_graph_context": (C.c_int, [C.c_int, C.c_int64] + [C.c_void_p] * 6 + [C.c_int64]),
@@ -82,7 +83,7 @@ SIGNATURES = {
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m clusterfusionplus_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python clusterfusionplus_b200/build.py` "
             "(nvcc, sm_100a). There is no fallback implementation.")
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

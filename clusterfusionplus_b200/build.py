@@ -1,6 +1,6 @@
 """Build libclusterfusion_b200.so in-tree with nvcc for sm_100a.
 
-    python -m clusterfusionplus_b200.build [--force] [--verbose]
+    python clusterfusionplus_b200/build.py [--force] [--verbose]
 
 The library has no torch dependency; it links the CUDA runtime statically and
 finds the driver's tensor-map encoder at run time.

@@ -302,6 +302,13 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     if (d.heads > c.grid) return fail(CF_ERR_UNSUPPORTED, "more heads (%d) than CTAs (%d)", d.heads, c.grid);
     if (ceil_div(d.hidden / GRAN, c.grid / c.cs) * GRAN > MAX_P3_ROWS)
         return fail(CF_ERR_UNSUPPORTED, "hidden %d too wide for %d clusters", d.hidden, c.grid / c.cs);
+    {
+        const int kco = ceil_div(d.heads * d.head_dim, KCHUNK);
+        const int hpc = ceil_div(KCHUNK, d.head_dim) + 1;
+        const int pstr = ceil_div(c.grid, d.heads) + 2;
+        if (pstr > MAX_PARTS || ceil_div(kco, c.cs) * hpc * pstr > WTS_SLOTS)
+            return fail(CF_ERR_UNSUPPORTED, "attention merge table too small for %d heads on %d CTAs", d.heads, c.grid);
+    }
     rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats);
     if (rc != CF_OK) return rc;
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
@@ -606,6 +613,34 @@ int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO*
 int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
                                   void* stream) {
     return run_layer(model, w, io, seq_len, stream, true);
+}
+
+int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, int phase_mask,
+                        void* stream) {
+    CfDims d;
+    int rc = model_dims(model, &d);
+    if (rc) return rc;
+    if ((rc = check_layer_args(w, io, seq_len, true, true))) return rc;
+    if (phase_mask <= 0 || phase_mask > (PH_P1 | PH_P2 | PH_P3)) return fail(CF_ERR_INVALID, "phase_mask %d", phase_mask);
+    DeviceState* ds;
+    if ((rc = get_device(&ds))) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LayerDesc* desc;
+    if ((rc = cached_desc(*ds, d, *w, io->k_cache, io->v_cache, io->kv_rows, st, &desc))) return rc;
+    Params p;
+    base_params(p, d, ds->ws);
+    p.layers = desc;
+    p.n_layers = 1;
+    p.p3_flags = F3_FULL;
+    p.phase_mask = phase_mask;
+    p.x_in = static_cast<const __half*>(io->input);
+    p.out = static_cast<__half*>(io->output);
+    p.k_new = static_cast<__half*>(io->k_new);
+    p.v_new = static_cast<__half*>(io->v_new);
+    p.cos = io->cos;
+    p.sin = io->sin;
+    p.seq_host = static_cast<int>(seq_len);
+    return launch(*ds, d, p, st);
 }
 
 int cf_pythia_attention_only(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, void* stream) {

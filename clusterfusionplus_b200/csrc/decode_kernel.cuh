@@ -52,7 +52,9 @@ constexpr int NTHREADS = NCTHR + 32;        // + producer warp
 constexpr int KV_TILE = 64;                 // cache rows per attention item
 constexpr int MAXL = 4;                     // attention partial slots per CTA
 constexpr int MAX_P3_ROWS = 256;            // output rows one cluster may own in P3
-constexpr int MAX_H = 8192;                 // LayerNorm register staging limit
+constexpr int MAX_H = 4096;                 // LayerNorm register staging limit
+constexpr int WTS_SLOTS = 640;              // (attention chunk, head, partial) merge weights one CTA may need
+constexpr int MAX_PARTS = 64;               // partials one head may be split into
 
 enum : int { PH_P1 = 1, PH_P2 = 2, PH_P3 = 4, PH_P4 = 8 };
 enum : int {
@@ -154,7 +156,10 @@ struct Smem {
     uint8_t* ring;
     float* xbuf;
     float* red;     // 64
-    float* q_s;     // 128
+    float* q_s;     // 128: scaled, rotated query of the current head
+    float* kv_s;    // 256: new token's key (rotated) and value, fp16-rounded
+    float* wts;     // WTS_SLOTS merge weights
+    int* offs;      // WTS_SLOTS offsets of the partials they weigh
     float* part_s;  // MAX_P3_ROWS
     float* recv;    // MAX_P3_ROWS
     uint64_t* full;
@@ -165,7 +170,7 @@ struct Smem {
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
+           (64 + 128 + 256 + 2 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -174,7 +179,10 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.xbuf = reinterpret_cast<float*>(base + static_cast<size_t>(nstage) * STAGE_BYTES);
     s.red = s.xbuf + xbuf_floats;
     s.q_s = s.red + 64;
-    s.part_s = s.q_s + 128;
+    s.kv_s = s.q_s + 128;
+    s.wts = s.kv_s + 256;
+    s.offs = reinterpret_cast<int*>(s.wts + WTS_SLOTS);
+    s.part_s = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
     s.recv = s.part_s + MAX_P3_ROWS;
     s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
     s.empty = s.full + MAX_STAGES;
@@ -286,7 +294,17 @@ __device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned& epoch,
 __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half* gamma, const __half* beta, int H,
                                                    float* xbuf, float* red, int tid, bool have_stats) {
     float xv[MAX_H / (NCTHR * 8)][8];
+    uint4 graw[MAX_H / (NCTHR * 8)], braw[MAX_H / (NCTHR * 8)];
     const int nvec = H >> 3;
+    // gamma / beta do not depend on the statistics: fetch them with x
+#pragma unroll
+    for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            graw[j] = __ldg(reinterpret_cast<const uint4*>(gamma + v * 8));
+            braw[j] = __ldg(reinterpret_cast<const uint4*>(beta + v * 8));
+        }
+    }
 #pragma unroll
     for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
         const int v = j * NCTHR + tid;
@@ -338,10 +356,8 @@ __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half
     for (int j = 0; j < MAX_H / (NCTHR * 8); ++j) {
         const int v = j * NCTHR + tid;
         if (v < nvec) {
-            const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gamma + v * 8));
-            const uint4 braw = __ldg(reinterpret_cast<const uint4*>(beta + v * 8));
-            const __half2* g2 = reinterpret_cast<const __half2*>(&graw);
-            const __half2* b2 = reinterpret_cast<const __half2*>(&braw);
+            const __half2* g2 = reinterpret_cast<const __half2*>(&graw[j]);
+            const __half2* b2 = reinterpret_cast<const __half2*>(&braw[j]);
             float o[8];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -633,8 +649,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             // ------------------------------------------------------------ P2
             if (p.phase_mask & PH_P2) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
-                // new token: RoPE, cache append, and its own softmax partial
-                if (warp == 0) {
+                // Empty cache (seq == 0): there are no items, so the head's owner CTA turns the
+                // new token into the head's only partial.  Otherwise the CTA that streams the
+                // head's last chunk folds the new token in (below).
+                if (nch == 0 && warp == 0) {
                     for (int h = 0; h < NH; ++h) {
                         if (head_owner(h, NH, G) != cta) continue;
                         const float* qv = p.qkv_f32 + h * 3 * D;
@@ -707,7 +725,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     if (h != cur_h) {
                         if (cur_h >= 0) flush(cur_h);
                         cur_h = h;
-                        if (tid < D) sm.q_s[tid] = rope_elem(p.qkv_f32 + h * 3 * D, tid, R, cosr, sinr) * qscale;
+                        // q for every CTA on this head; k, v (fp16-rounded, appended to the
+                        // cache) only where the head's last chunk is streamed
+                        const bool has_last = (h + 1) * nch - 1 < t2b;
+                        const float* qv = p.qkv_f32 + h * 3 * D;
+                        for (int e = tid; e < (has_last ? 3 * D : D); e += NCTHR) {
+                            const int part = e / D, d = e - part * D;
+                            if (part == 0) {
+                                sm.q_s[d] = rope_elem(qv, d, R, cosr, sinr) * qscale;
+                            } else {
+                                const float val = (part == 1) ? rope_elem(qv + D, d, R, cosr, sinr)
+                                                              : ld_cg_f32(qv + 2 * D + d);
+                                const __half h16 = __float2half_rn(val);
+                                sm.kv_s[(part - 1) * D + d] = __half2float(h16);
+                                const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
+                                if (part == 1) {
+                                    L->k_cache[off] = h16;
+                                    if (p.k_new) p.k_new[h * D + d] = h16;
+                                } else {
+                                    L->v_cache[off] = h16;
+                                    if (p.v_new) p.v_new[h * D + d] = h16;
+                                }
+                            }
+                        }
                         consumer_sync(NCTHR);
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
@@ -774,6 +814,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                     co.release_stage();
+                    // the token being decoded: one extra row after the head's last chunk
+                    if (ch == nch - 1 && warp == 0 && hw == 0) {
+                        float sn = 0.f;
+                        if (dim_ok) {
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) sn = fmaf(qreg[k], sm.kv_s[l16 * 8 + k], sn);
+                        }
+#pragma unroll
+                        for (int o = 8; o > 0; o >>= 1) sn += __shfl_xor_sync(0x0000ffffu, sn, o);
+                        const float mx = fmaxf(m_run, sn);
+                        const float sc = exp2f(m_run - mx), pn = exp2f(sn - mx);
+                        l_run = fmaf(l_run, sc, pn);
+                        if (dim_ok) {
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) acc[k] = fmaf(acc[k], sc, pn * sm.kv_s[D + l16 * 8 + k]);
+                        }
+                        m_run = mx;
+                    }
                 }
                 if (cur_h >= 0) flush(cur_h);
                 need_barrier = true;
@@ -782,51 +840,147 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             // ------------------------------------------------------------ P3
             if (p.phase_mask & PH_P3) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
-                // this CTA's K slice of [attn ; mid] as fp32 in xbuf, chunk-major
-                for (int i = 0; i < my3; ++i) {
-                    const int q = me + i * CS;
-                    float val = 0.f;
-                    if (q < KCo) {
-                        const int e = q * KCHUNK + tid;
-                        if (e < KVW) {
-                            const int h = e / D, d = e - h * D;
-                            const float* pn = p.attn_new + h * (D + 2);
-                            float M = ld_cg_f32(pn + D);
-                            int ia = 0, ib = -1;
-                            if (nch > 0) {
-                                ia = part_of(h * nch, T2, G);
-                                ib = part_of((h + 1) * nch - 1, T2, G);
-                            }
-                            // CTAs strictly between ia and ib may own no item at all (T2 < G)
-                            for (int c = ia; c <= ib; ++c) {
-                                const int b0 = part_begin(c, T2, G);
-                                if (part_begin(c + 1, T2, G) == b0) continue;
-                                const int loc = h - b0 / nch;
-                                M = fmaxf(M, ld_cg_f32(p.attn_part + (static_cast<size_t>(c) * MAXL + loc) * (D + 2) + D));
-                            }
-                            float w = exp2f(ld_cg_f32(pn + D) - M);
-                            float den = w * ld_cg_f32(pn + D + 1);
-                            float num = w * ld_cg_f32(pn + d);
-                            for (int c = ia; c <= ib; ++c) {
-                                const int b0 = part_begin(c, T2, G);
-                                if (part_begin(c + 1, T2, G) == b0) continue;
-                                const int loc = h - b0 / nch;
-                                const float* pp = p.attn_part + (static_cast<size_t>(c) * MAXL + loc) * (D + 2);
-                                w = exp2f(ld_cg_f32(pp + D) - M);
-                                den = fmaf(w, ld_cg_f32(pp + D + 1), den);
-                                num = fmaf(w, ld_cg_f32(pp + d), num);
-                            }
-                            val = num / den;
-                        }
-                    } else {
-                        const int e = (q - KCo) * KCHUNK + tid;
-                        if (e < F) {
-                            val = (p.p3_flags & F3_MID_F16) ? __half2float(ld_cg_f16(p.mid_f16_in + e))
-                                                            : ld_cg_f32(p.mid_f32 + e);
+                // ---- this CTA's K slice of [attn ; mid] as fp32 in xbuf, chunk-major.
+                // Everything here is L2 latency, so loads are issued in wide batches.
+                const int nattn = (KCo > me) ? ceil_div(KCo - me, CS) : 0;  // my chunks that hold attention
+                // (1) MLP intermediate: asynchronous 16-byte copies straight into xbuf
+                if (!(p.p3_flags & F3_MID_F16)) {
+                    const int nvec = (my3 - nattn) * (KCHUNK / 4);
+                    for (int v = tid; v < nvec; v += NCTHR) {
+                        const int i = nattn + v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                        const int e = (me + i * CS - KCo) * KCHUNK + k4 * 4;
+                        float* dst = sm.xbuf + i * KCHUNK + k4 * 4;
+                        if (e + 3 < F) {
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                                         "l"(p.mid_f32 + e) : "memory");
+                        } else {
+                            for (int k = 0; k < 4; ++k) dst[k] = (e + k < F) ? ld_cg_f32(p.mid_f32 + e + k) : 0.f;
                         }
                     }
-                    sm.xbuf[i * KCHUNK + tid] = val;
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                } else {
+                    for (int i0 = nattn; i0 < my3; i0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int ii = 0; ii < 8; ++ii) {
+                            const int e = (me + (i0 + ii) * CS - KCo) * KCHUNK + tid;
+                            v[ii] = (i0 + ii < my3 && e < F) ? __half2float(ld_cg_f16(p.mid_f16_in + e)) : 0.f;
+                        }
+#pragma unroll
+                        for (int ii = 0; ii < 8; ++ii)
+                            if (i0 + ii < my3) sm.xbuf[(i0 + ii) * KCHUNK + tid] = v[ii];
+                    }
                 }
+                // (2) softmax merge weights: one warp per (my attention chunk, head touching it)
+                constexpr int HPC = (KCHUNK + D - 1) / D + 1;
+                const int pstr = (nch == 0) ? 1 : min(MAX_PARTS, ceil_div(G, NH) + 2);
+                const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
+                for (int pair = warp; pair < nattn * HPC; pair += NCWARP) {
+                    const int i = pair / HPC, hh = pair - i * HPC;
+                    const int q = me + i * CS;
+                    const int h = (q * KCHUNK) / D + hh;
+                    const bool head_ok = h < NH && h * D < min((q + 1) * KCHUNK, KVW);
+                    int ia = 0, ib = -1;
+                    if (head_ok) {
+                        if (nch == 0) {
+                            ib = 0;
+                        } else {
+                            ia = part_of(h * nch, T2, G);
+                            ib = part_of((h + 1) * nch - 1, T2, G);
+                        }
+                    }
+                    float m[2], lq[2];
+                    int off[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int j = lane + 32 * u;
+                        off[u] = -1;
+                        m[u] = -INFINITY;
+                        lq[u] = 0.f;
+                        if (j < pstr && ia + j <= ib) {
+                            if (nch == 0) {
+                                off[u] = h * (D + 2);
+                            } else {
+                                const int c = ia + j;
+                                const int b0 = part_begin(c, T2, G);
+                                // CTAs between ia and ib may own no item at all (T2 < G)
+                                if (part_begin(c + 1, T2, G) != b0) off[u] = (c * MAXL + (h - b0 / nch)) * (D + 2);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (off[u] >= 0) {
+                            m[u] = ld_cg_f32(pbase + off[u] + D);
+                            lq[u] = ld_cg_f32(pbase + off[u] + D + 1);
+                        }
+                    }
+                    float M = fmaxf(m[0], m[1]);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                    float w[2], den = 0.f;
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        w[u] = (off[u] >= 0 && M > -INFINITY) ? exp2f(m[u] - M) : 0.f;
+                        den = fmaf(w[u], lq[u], den);
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+                    const float inv = (den > 0.f) ? 1.0f / den : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int j = lane + 32 * u;
+                        if (j < pstr) {
+                            sm.wts[pair * pstr + j] = w[u] * inv;
+                            sm.offs[pair * pstr + j] = off[u];
+                        }
+                    }
+                }
+                consumer_sync(NCTHR);
+                // (3) merged attention output, four chunks x eight partials of loads in flight
+                for (int i0 = 0; i0 < nattn; i0 += 4) {
+                    float val[4] = {0.f, 0.f, 0.f, 0.f};
+                    int wrow[4], dd[4];
+#pragma unroll
+                    for (int ii = 0; ii < 4; ++ii) {
+                        const int q = me + (i0 + ii) * CS;
+                        const int e = q * KCHUNK + tid;
+                        wrow[ii] = -1;
+                        dd[ii] = 0;
+                        if (i0 + ii < nattn && e < KVW) {
+                            const int h = e / D;
+                            dd[ii] = e - h * D;
+                            wrow[ii] = ((i0 + ii) * HPC + (h - (q * KCHUNK) / D)) * pstr;
+                        }
+                    }
+                    for (int j0 = 0; j0 < pstr; j0 += 8) {
+                        float v[4][8];
+#pragma unroll
+                        for (int ii = 0; ii < 4; ++ii) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                v[ii][jj] = 0.f;
+                                if (wrow[ii] >= 0 && j0 + jj < pstr) {
+                                    const int o = sm.offs[wrow[ii] + j0 + jj];
+                                    if (o >= 0) v[ii][jj] = ld_cg_f32(pbase + o + dd[ii]);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int ii = 0; ii < 4; ++ii) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                // slots without a partial hold weight 0; v is 0 where no load was issued
+                                const bool on = wrow[ii] >= 0 && j0 + jj < pstr;
+                                val[ii] = fmaf(on ? sm.wts[wrow[ii] + j0 + jj] : 0.f, v[ii][jj], val[ii]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int ii = 0; ii < 4; ++ii)
+                        if (i0 + ii < nattn) sm.xbuf[(i0 + ii) * KCHUNK + tid] = val[ii];
+                }
+                asm volatile("cp.async.wait_all;" ::: "memory");
                 consumer_sync(NCTHR);
 
                 const int cnt = g3b - g3a;

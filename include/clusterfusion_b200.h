@@ -98,6 +98,13 @@ int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO*
 int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
                                   void* stream);
 
+/* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
+ * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one
+ * launch, reading what earlier phases left in the library's scratch.  Used by the
+ * profiling scripts to time phases in isolation; no counterpart in the reference. */
+int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, int phase_mask,
+                        void* stream);
+
 /* Attention half: io->attn_output = dense(attention) + o_bias, io->mlp_intermediate =
  * gelu(up(post_ln(x))), io->k_new / io->v_new.  mlp_down_* of `w` may be NULL.
  * Replaces pythia_2b8_attention_only_sm120 (include/pybind.cpp:154-171;
