@@ -177,6 +177,8 @@ struct DeviceState {
     Workspace ws;
     std::map<DescKey, LayerDesc*> desc_cache;
     std::map<std::pair<int, int64_t>, GraphCtx> contexts;
+    unsigned long long* trace = nullptr;  // diagnostics: timeline buffer applied to every launch
+    size_t trace_slots = 0;
 };
 
 std::mutex g_mu;
@@ -313,6 +315,8 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     if (rc != CF_OK) return rc;
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
     const void* fn = kernel_ptr(d.head_dim, c.cs);
+    p.trace = nullptr;
+    if (ds.trace && static_cast<size_t>(c.grid) * (p.n_layers + 1) * TRACE_EVENTS <= ds.trace_slots) p.trace = ds.trace;
     for (int attempt = 0; attempt < 2; ++attempt) {
         cudaLaunchConfig_t lc = {};
         lc.gridDim = dim3(c.grid);
@@ -641,6 +645,15 @@ int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io,
     p.sin = io->sin;
     p.seq_host = static_cast<int>(seq_len);
     return launch(*ds, d, p, st);
+}
+
+int cf_debug_set_trace(void* device_buffer, int64_t n_slots) {
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    ds->trace = static_cast<unsigned long long*>(device_buffer);
+    ds->trace_slots = device_buffer ? static_cast<size_t>(n_slots) : 0;
+    return CF_OK;
 }
 
 int cf_pythia_attention_only(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, void* stream) {

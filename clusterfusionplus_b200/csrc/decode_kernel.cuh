@@ -126,7 +126,18 @@ struct Params {
     int* token_out;    // next token id (may alias token_in)
     int* seq_inc;      // optional: *seq_inc += 1 at the end of the launch
     int vocab_offset;  // added to the argmax index (vocabulary shards)
+    // optional timeline: [grid][n_layers + 1][TRACE_EVENTS] globaltimer stamps (diagnostics)
+    unsigned long long* trace;
 };
+
+constexpr int TRACE_EVENTS = 16;
+enum : int {
+    TR_START = 0, TR_LN_DONE, TR_P1_DONE, TR_BAR1, TR_P2_DONE, TR_BAR2, TR_X3_BUILT, TR_P3_GEMV, TR_P3_DONE,
+    TR_PROD_P1 = 10, TR_PROD_P2, TR_PROD_P3,
+};
+__device__ __forceinline__ void trace_mark(const Params& p, int cta, int layer, int ev) {
+    if (p.trace) p.trace[(static_cast<size_t>(cta) * (p.n_layers + 1) + layer) * TRACE_EVENTS + ev] = globaltimer_ns();
+}
 
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // units [part_begin(i), part_begin(i+1)) of `total` belong to part i of `parts`
@@ -158,8 +169,9 @@ struct Smem {
     float* red;     // 64
     float* q_s;     // 128: scaled, rotated query of the current head
     float* kv_s;    // 256: new token's key (rotated) and value, fp16-rounded
-    float* wts;     // WTS_SLOTS merge weights
-    int* offs;      // WTS_SLOTS offsets of the partials they weigh
+    float* pm;      // WTS_SLOTS running maxima of the partials this CTA merges
+    float* pl;      // WTS_SLOTS their denominators
+    int* offs;      // WTS_SLOTS their offsets in the partial buffer (-1: none), fixed for a launch
     float* part_s;  // MAX_P3_ROWS
     float* recv;    // MAX_P3_ROWS
     uint64_t* full;
@@ -170,7 +182,7 @@ struct Smem {
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + 256 + 2 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
+           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -180,8 +192,9 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.red = s.xbuf + xbuf_floats;
     s.q_s = s.red + 64;
     s.kv_s = s.q_s + 128;
-    s.wts = s.kv_s + 256;
-    s.offs = reinterpret_cast<int*>(s.wts + WTS_SLOTS);
+    s.pm = s.kv_s + 256;
+    s.pl = s.pm + WTS_SLOTS;
+    s.offs = reinterpret_cast<int*>(s.pl + WTS_SLOTS);
     s.part_s = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
     s.recv = s.part_s + MAX_P3_ROWS;
     s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
@@ -509,9 +522,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     // ---- static work split (identical on producer and consumer side)
     const int KC1 = ceil_div(H, KCHUNK);
     const int NGq = (3 * KVW) / GRAN, NGu = F / GRAN, NG1 = NGq + NGu;
-    const int g1a = part_begin(cta, NG1, G), g1b = part_begin(cta + 1, NG1, G);
-    const int qa = min(g1a, NGq), qb = min(g1b, NGq);              // QKV granules [qa, qb)
-    const int ua = max(g1a, NGq) - NGq, ub = max(g1b, NGq) - NGq;  // up granules [ua, ub)
+    // CTAs [0, Gq) share the QKV rows, CTAs [Gq, G) the MLP-up rows, in proportion to
+    // their sizes, so no CTA needs both LayerNorms or a ragged extra round.
+    int Gq = (NGu == 0) ? G : (NGq == 0 ? 0 : static_cast<int>((static_cast<long long>(G) * NGq + NG1 / 2) / NG1));
+    if (NGq > 0 && NGu > 0) Gq = max(1, min(G - 1, Gq));
+    int qa = 0, qb = 0, ua = 0, ub = 0;  // QKV granules [qa, qb), up granules [ua, ub)
+    if (cta < Gq) {
+        qa = part_begin(cta, NGq, Gq);
+        qb = part_begin(cta + 1, NGq, Gq);
+    } else {
+        ua = part_begin(cta - Gq, NGu, G - Gq);
+        ub = part_begin(cta - Gq + 1, NGu, G - Gq);
+    }
     const int nch = ceil_div(seq, KV_TILE);
     const int T2 = NH * nch;
     const int t2a = part_begin(cta, T2, G), t2b = part_begin(cta + 1, T2, G);
@@ -523,6 +545,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     const int KCd = (p.p3_flags & F3_USE_DOWN) ? ceil_div(F, KCHUNK) : 0;
     const int KC3 = KCo + KCd;
     const int my3 = (KC3 > me) ? ceil_div(KC3 - me, CS) : 0;  // chunks me, me+CS, ...
+    // attention merge tables (P3): my chunks that hold attention, heads touching a
+    // chunk, partial slots per head
+    constexpr int HPC = (KCHUNK + D - 1) / D + 1;
+    const int nattn = (KCo > me) ? ceil_div(KCo - me, CS) : 0;
+    const int pstr = (nch == 0) ? 1 : min(MAX_PARTS, ceil_div(G, NH) + 2);
     int NG4 = 0, g4a = 0, g4b = 0;
     if (p.phase_mask & PH_P4) {
         NG4 = ceil_div(p.tail->vocab, GRAN);
@@ -546,9 +573,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (p.phase_mask & PH_P1) {
                     pr.rows_phase(&L->tm_qkv, qa, qb - qa, KC1);
                     pr.rows_phase(&L->tm_up, ua, ub - ua, KC1);
+                    trace_mark(p, cta, l, TR_PROD_P1);
                 }
                 if (p.phase_mask & PH_P2) {
                     for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(&L->tm_k, &L->tm_v, t / nch, t % nch);
+                    trace_mark(p, cta, l, TR_PROD_P2);
                 }
                 if (p.phase_mask & PH_P3) {
                     const int cnt = g3b - g3a;
@@ -565,6 +594,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             g += n;
                         }
                     }
+                    trace_mark(p, cta, l, TR_PROD_P3);
                 }
             }
             if (p.phase_mask & PH_P4) pr.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
@@ -607,6 +637,32 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
         bool need_barrier = false;  // a phase of this launch wrote data the next one reads
 
+        // Which partial feeds which of my attention chunks depends only on (grid, seq):
+        // tabulate it once per launch.
+        if (p.phase_mask & PH_P3) {
+            for (int it = tid; it < nattn * HPC * pstr; it += NCTHR) {
+                const int pair = it / pstr, j = it - pair * pstr;
+                const int i = pair / HPC, hh = pair - i * HPC;
+                const int q = me + i * CS;
+                const int h = (q * KCHUNK) / D + hh;
+                int off = -1;
+                if (h < NH && h * D < min((q + 1) * KCHUNK, KVW)) {
+                    if (nch == 0) {
+                        if (j == 0) off = h * (D + 2);
+                    } else {
+                        const int c = part_of(h * nch, T2, G) + j;
+                        if (c <= part_of((h + 1) * nch - 1, T2, G)) {
+                            const int b0 = part_begin(c, T2, G);
+                            // CTAs between the first and last may own no item at all (T2 < G)
+                            if (part_begin(c + 1, T2, G) != b0) off = (c * MAXL + (h - b0 / nch)) * (D + 2);
+                        }
+                    }
+                }
+                sm.offs[it] = off;
+            }
+            consumer_sync(NCTHR);
+        }
+
         const __half* x_first = p.embed ? (p.embed + static_cast<size_t>(__ldcg(p.token_in)) * H) : p.x_in;
 
         for (int l = 0; l < p.n_layers; ++l) {
@@ -617,10 +673,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             // ------------------------------------------------------------ P1
             if (p.phase_mask & PH_P1) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                if (tid == 0) {
+                    trace_mark(p, cta, l, TR_START);
+                    if (p.trace) {
+                        unsigned smid;
+                        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                        p.trace[(static_cast<size_t>(cta) * (p.n_layers + 1) + l) * TRACE_EVENTS + 9] = smid;
+                    }
+                }
                 bool have_stats = false;
                 if (qb > qa) {
                     layer_norm_to_smem(x, L->ln_w, L->ln_b, H, sm.xbuf, sm.red, tid, have_stats);
                     have_stats = true;
+                    if (tid == 0) trace_mark(p, cta, l, TR_LN_DONE);
                     const __half* bq = L->b_qkv;
                     float* dst = p.qkv_f32;
                     const int row0 = qa * GRAN;
@@ -643,12 +708,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         if (dst16) dst16[row] = __float2half_rn(a);
                     });
                 }
+                if (tid == 0) trace_mark(p, cta, l, TR_P1_DONE);
                 need_barrier = true;
             }
 
             // ------------------------------------------------------------ P2
             if (p.phase_mask & PH_P2) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                if (tid == 0) trace_mark(p, cta, l, TR_BAR1);
                 // Empty cache (seq == 0): there are no items, so the head's owner CTA turns the
                 // new token into the head's only partial.  Otherwise the CTA that streams the
                 // head's last chunk folds the new token in (below).
@@ -834,15 +901,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                 }
                 if (cur_h >= 0) flush(cur_h);
+                if (tid == 0) trace_mark(p, cta, l, TR_P2_DONE);
                 need_barrier = true;
             }
 
             // ------------------------------------------------------------ P3
             if (p.phase_mask & PH_P3) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                if (tid == 0) trace_mark(p, cta, l, TR_BAR2);
                 // ---- this CTA's K slice of [attn ; mid] as fp32 in xbuf, chunk-major.
                 // Everything here is L2 latency, so loads are issued in wide batches.
-                const int nattn = (KCo > me) ? ceil_div(KCo - me, CS) : 0;  // my chunks that hold attention
                 // (1) MLP intermediate: asynchronous 16-byte copies straight into xbuf
                 if (!(p.p3_flags & F3_MID_F16)) {
                     const int nvec = (my3 - nattn) * (KCHUNK / 4);
@@ -871,78 +939,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (i0 + ii < my3) sm.xbuf[(i0 + ii) * KCHUNK + tid] = v[ii];
                     }
                 }
-                // (2) softmax merge weights: one warp per (my attention chunk, head touching it)
-                constexpr int HPC = (KCHUNK + D - 1) / D + 1;
-                const int pstr = (nch == 0) ? 1 : min(MAX_PARTS, ceil_div(G, NH) + 2);
+                // (2) attention merge.  offs[] (which partials feed which of my chunks) was
+                // tabulated at kernel start.  One L2 round trip: every thread fetches the
+                // (max, denominator) pair of one table entry and, without waiting, the
+                // numerators of its elements; then one thread per entry turns the pairs into
+                // normalised weights, and the elements are weighted sums.
                 const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
-                for (int pair = warp; pair < nattn * HPC; pair += NCWARP) {
-                    const int i = pair / HPC, hh = pair - i * HPC;
-                    const int q = me + i * CS;
-                    const int h = (q * KCHUNK) / D + hh;
-                    const bool head_ok = h < NH && h * D < min((q + 1) * KCHUNK, KVW);
-                    int ia = 0, ib = -1;
-                    if (head_ok) {
-                        if (nch == 0) {
-                            ib = 0;
-                        } else {
-                            ia = part_of(h * nch, T2, G);
-                            ib = part_of((h + 1) * nch - 1, T2, G);
-                        }
-                    }
-                    float m[2], lq[2];
-                    int off[2];
+                const int nent = nattn * HPC * pstr;
+                constexpr int ML_ITERS = (WTS_SLOTS + NCTHR - 1) / NCTHR;
+                float mreg[ML_ITERS], lreg[ML_ITERS];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int j = lane + 32 * u;
-                        off[u] = -1;
-                        m[u] = -INFINITY;
-                        lq[u] = 0.f;
-                        if (j < pstr && ia + j <= ib) {
-                            if (nch == 0) {
-                                off[u] = h * (D + 2);
-                            } else {
-                                const int c = ia + j;
-                                const int b0 = part_begin(c, T2, G);
-                                // CTAs between ia and ib may own no item at all (T2 < G)
-                                if (part_begin(c + 1, T2, G) != b0) off[u] = (c * MAXL + (h - b0 / nch)) * (D + 2);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (off[u] >= 0) {
-                            m[u] = ld_cg_f32(pbase + off[u] + D);
-                            lq[u] = ld_cg_f32(pbase + off[u] + D + 1);
-                        }
-                    }
-                    float M = fmaxf(m[0], m[1]);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-                    float w[2], den = 0.f;
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        w[u] = (off[u] >= 0 && M > -INFINITY) ? exp2f(m[u] - M) : 0.f;
-                        den = fmaf(w[u], lq[u], den);
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-                    const float inv = (den > 0.f) ? 1.0f / den : 0.f;
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int j = lane + 32 * u;
-                        if (j < pstr) {
-                            sm.wts[pair * pstr + j] = w[u] * inv;
-                            sm.offs[pair * pstr + j] = off[u];
+                for (int k = 0; k < ML_ITERS; ++k) {
+                    const int it = tid + k * NCTHR;
+                    mreg[k] = -INFINITY;
+                    lreg[k] = 0.f;
+                    if (it < nent) {
+                        const int o = sm.offs[it];
+                        if (o >= 0) {
+                            mreg[k] = ld_cg_f32(pbase + o + D);
+                            lreg[k] = ld_cg_f32(pbase + o + D + 1);
                         }
                     }
                 }
-                consumer_sync(NCTHR);
-                // (3) merged attention output, four chunks x eight partials of loads in flight
-                for (int i0 = 0; i0 < nattn; i0 += 4) {
-                    float val[4] = {0.f, 0.f, 0.f, 0.f};
-                    int wrow[4], dd[4];
+                bool tables_ready = false;
+                for (int i0 = 0; i0 < nattn || !tables_ready; i0 += 8) {
+                    int wrow[8], dd[8];
 #pragma unroll
-                    for (int ii = 0; ii < 4; ++ii) {
+                    for (int ii = 0; ii < 8; ++ii) {
                         const int q = me + (i0 + ii) * CS;
                         const int e = q * KCHUNK + tid;
                         wrow[ii] = -1;
@@ -953,10 +976,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             wrow[ii] = ((i0 + ii) * HPC + (h - (q * KCHUNK) / D)) * pstr;
                         }
                     }
-                    for (int j0 = 0; j0 < pstr; j0 += 8) {
-                        float v[4][8];
+                    float val[8];
 #pragma unroll
-                        for (int ii = 0; ii < 4; ++ii) {
+                    for (int ii = 0; ii < 8; ++ii) val[ii] = 0.f;
+                    for (int j0 = 0; j0 < pstr; j0 += 8) {
+                        float v[8][8];
+#pragma unroll
+                        for (int ii = 0; ii < 8; ++ii) {
 #pragma unroll
                             for (int jj = 0; jj < 8; ++jj) {
                                 v[ii][jj] = 0.f;
@@ -966,22 +992,70 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                                 }
                             }
                         }
+                        if (!tables_ready) {
 #pragma unroll
-                        for (int ii = 0; ii < 4; ++ii) {
+                            for (int k = 0; k < ML_ITERS; ++k) {
+                                const int it = tid + k * NCTHR;
+                                if (it < nent) {
+                                    sm.pm[it] = mreg[k];
+                                    sm.pl[it] = lreg[k];
+                                }
+                            }
+                            consumer_sync(NCTHR);
+                            // weight of entry `it` inside its (chunk, head) row, normalised
+                            float wn[ML_ITERS];
+#pragma unroll
+                            for (int k = 0; k < ML_ITERS; ++k) {
+                                const int it = tid + k * NCTHR;
+                                wn[k] = 0.f;
+                                if (it < nent && mreg[k] > -INFINITY) {
+                                    const int r0 = (it / pstr) * pstr;
+                                    float M = -INFINITY, den = 0.f;
+                                    for (int j = 0; j < pstr; ++j) M = fmaxf(M, sm.pm[r0 + j]);
+                                    for (int j = 0; j < pstr; ++j) {
+                                        const float mj = sm.pm[r0 + j];
+                                        if (mj > -INFINITY) den = fmaf(exp2f(mj - M), sm.pl[r0 + j], den);
+                                    }
+                                    wn[k] = exp2f(mreg[k] - M) / den;
+                                }
+                            }
+                            consumer_sync(NCTHR);  // everyone has read pm before it becomes the weight table
+#pragma unroll
+                            for (int k = 0; k < ML_ITERS; ++k) {
+                                const int it = tid + k * NCTHR;
+                                if (it < nent) sm.pm[it] = wn[k];
+                            }
+                            consumer_sync(NCTHR);
+                            tables_ready = true;
+                        }
+#pragma unroll
+                        for (int ii = 0; ii < 8; ++ii) {
 #pragma unroll
                             for (int jj = 0; jj < 8; ++jj) {
-                                // slots without a partial hold weight 0; v is 0 where no load was issued
                                 const bool on = wrow[ii] >= 0 && j0 + jj < pstr;
-                                val[ii] = fmaf(on ? sm.wts[wrow[ii] + j0 + jj] : 0.f, v[ii][jj], val[ii]);
+                                val[ii] = fmaf(on ? sm.pm[wrow[ii] + j0 + jj] : 0.f, v[ii][jj], val[ii]);
                             }
                         }
                     }
 #pragma unroll
-                    for (int ii = 0; ii < 4; ++ii)
+                    for (int ii = 0; ii < 8; ++ii)
                         if (i0 + ii < nattn) sm.xbuf[(i0 + ii) * KCHUNK + tid] = val[ii];
+                }
+                // (3) what the epilogue adds to this thread's output row, fetched early
+                float epi_add = 0.f;
+                {
+                    const int nrows_e = (g3b - g3a) * GRAN;
+                    if (me + tid * CS < nrows_e) {
+                        const int row = g3a * GRAN + me + tid * CS;
+                        if (p.p3_flags & F3_ADD_BO) epi_add += __half2float(__ldg(L->b_o + row));
+                        if (p.p3_flags & F3_ADD_BDOWN) epi_add += __half2float(__ldg(L->b_down + row));
+                        if (p.p3_flags & F3_ADD_X) epi_add += __half2float(ld_cg_f16(x + row));
+                        if (p.extra_add_f16) epi_add += __half2float(ld_cg_f16(p.extra_add_f16 + row));
+                    }
                 }
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 consumer_sync(NCTHR);
+                if (tid == 0) trace_mark(p, cta, l, TR_X3_BUILT);
 
                 const int cnt = g3b - g3a;
                 const int nrows = cnt * GRAN;
@@ -993,18 +1067,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         for (int t = tid; t < nrows; t += NCTHR) sm.part_s[t] = 0.f;
                     }
                 }
+                if (tid == 0) trace_mark(p, cta, l, TR_P3_GEMV);
                 const int stride = MAX_P3_ROWS / CS;
                 dsm::reduce_scatter_push<CS>(sm.part_s, sm.recv, stride, nrows, sm.xbar, xparity, tid, NCTHR, ab);
                 xparity ^= 1u;
-                for (int j = tid; me + j * CS < nrows; j += NCTHR) {
-                    const int row = g3a * GRAN + me + j * CS;
-                    float v = dsm::tree_sum<CS>(sm.recv, stride, j);
-                    if (p.p3_flags & F3_ADD_BO) v += __half2float(__ldg(L->b_o + row));
-                    if (p.p3_flags & F3_ADD_BDOWN) v += __half2float(__ldg(L->b_down + row));
-                    if (p.p3_flags & F3_ADD_X) v += __half2float(ld_cg_f16(x + row));
-                    if (p.extra_add_f16) v += __half2float(ld_cg_f16(p.extra_add_f16 + row));
-                    y[row] = __float2half_rn(v);
+                // one output row per thread at most (MAX_P3_ROWS / CS <= consumer threads)
+                if (me + tid * CS < nrows) {
+                    const int row = g3a * GRAN + me + tid * CS;
+                    y[row] = __float2half_rn(dsm::tree_sum<CS>(sm.recv, stride, tid) + epi_add);
                 }
+                if (tid == 0) trace_mark(p, cta, l, TR_P3_DONE);
                 need_barrier = true;
             }
         }

@@ -105,6 +105,13 @@ int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLa
 int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, int phase_mask,
                         void* stream);
 
+/* Diagnostic: while a buffer is set, every launch on the current device stamps the
+ * nanosecond timer at its phase boundaries into it, laid out
+ * [CTA][layer (n_layers + 1 rows)][16 events] uint64; n_slots = its length in
+ * elements; a launch that would not fit leaves it untouched.  NULL switches it
+ * off.  No counterpart in the reference. */
+int cf_debug_set_trace(void* device_buffer, int64_t n_slots);
+
 /* Attention half: io->attn_output = dense(attention) + o_bias, io->mlp_intermediate =
  * gelu(up(post_ln(x))), io->k_new / io->v_new.  mlp_down_* of `w` may be NULL.
  * Replaces pythia_2b8_attention_only_sm120 (include/pybind.cpp:154-171;
