@@ -1,0 +1,116 @@
+"""Host-side checks that need no GPU: the C ABI exports what the header declares,
+the Python operator surface mirrors the reference's, argument validation, and the
+static work split the kernel uses."""
+import ctypes
+import inspect
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "clusterfusion_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from clusterfusionplus_b200 import _lib
+    syms = header_symbols()
+    assert len(syms) >= 20
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in syms:
+        assert hasattr(raw, name), f"{name} declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == syms
+
+
+def test_error_string_without_gpu():
+    """No CPU fallback: on a box without a CUDA device the entry points fail and say why."""
+    from clusterfusionplus_b200 import _lib
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    d = _lib.CfDims()
+    assert _lib.lib.cf_model_dims(1, ctypes.byref(d)) == 0 and d.hidden == 4096 and d.head_dim == 128
+    assert _lib.lib.cf_model_dims(7, ctypes.byref(d)) != 0
+    assert "unknown model" in _lib.last_error()
+    s = ctypes.c_int(0)
+    assert _lib.lib.cf_get_status(ctypes.byref(s)) != 0
+    assert _lib.last_error() != ""
+
+
+REFERENCE_SURFACE = [
+    # names of include/pybind.cpp:285-297 of the reference, with their arity
+    ("pythia_2b8_decoder_layer", 18), ("pythia_2b8_decoder_layer_split", 18), ("pythia_2b8_attention_only", 16),
+    ("pythia_2b8_mlp_only", 5), ("pythia_2b8_create_graph_context", 8), ("pythia_2b8_graph_decode_step", 15),
+    ("pythia_2b8_destroy_graph_context", 1), ("pythia_6b9_decoder_layer", 18), ("pythia_6b9_create_graph_context", 8),
+    ("pythia_6b9_graph_decode_step", 15), ("pythia_6b9_destroy_graph_context", 1),
+]
+
+
+def test_drop_in_module_surface():
+    import clusterfusion
+    for name, _ in REFERENCE_SURFACE:
+        assert callable(getattr(clusterfusion, name)), name
+    sig = inspect.signature(clusterfusion.pythia_2b8_attention_only)
+    assert len(sig.parameters) == 16
+    assert len(inspect.signature(clusterfusion.pythia_2b8_mlp_only).parameters) == 5
+
+
+def test_cpu_tensors_are_rejected():
+    import clusterfusion
+    H, F = 2560, 10240
+    z = lambda *s: torch.zeros(*s, dtype=torch.float16)
+    args = [z(1, H), z(3 * H, H), z(3 * H), z(H, H), z(H), z(8, H), z(8, H), z(H), z(H),
+            torch.zeros(20), torch.zeros(20), z(H), z(H), z(F, H), z(F), z(H, F), z(H), 3]
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        clusterfusion.pythia_2b8_decoder_layer(*args)
+
+
+# ---- mirror of the kernel's static split (decode_kernel.cuh: part_begin / part_of)
+def part_begin(i, total, parts):
+    return (i * total) // parts
+
+
+def part_of(t, total, parts):
+    return ((t + 1) * parts - 1) // total
+
+
+@pytest.mark.parametrize("total,parts", [(3584, 148), (2048, 148), (10, 4), (64, 148), (1, 148), (4096, 132), (512, 74)])
+def test_partition_is_exact_and_invertible(total, parts):
+    seen = 0
+    for i in range(parts):
+        a, b = part_begin(i, total, parts), part_begin(i + 1, total, parts)
+        assert a <= b
+        for t in range(a, b):
+            assert part_of(t, total, parts) == i
+        seen += b - a
+    assert seen == total
+    sizes = [part_begin(i + 1, total, parts) - part_begin(i, total, parts) for i in range(parts)]
+    assert max(sizes) - min(sizes) <= 1
+
+
+@pytest.mark.parametrize("NH,G", [(32, 148), (32, 132), (16, 148), (8, 148), (4, 148)])
+@pytest.mark.parametrize("seq", [1, 63, 64, 65, 1000, 4096, 8192, 20000])
+def test_attention_item_split_bounds(NH, G, seq):
+    """A CTA's items touch at most MAXL = 4 heads, a head is split into at most
+    ceil(G / NH) + 2 partials: the sizes the kernel's scratch is laid out for."""
+    nch = -(-seq // 64)
+    T = NH * nch
+    pstr = -(-G // NH) + 2
+    for c in range(G):
+        a, b = part_begin(c, T, G), part_begin(c + 1, T, G)
+        if b > a:
+            assert (b - 1) // nch - a // nch < 4
+    for h in range(NH):
+        ia, ib = part_of(h * nch, T, G), part_of((h + 1) * nch - 1, T, G)
+        assert ib - ia + 1 <= pstr
+        covered = 0
+        for c in range(ia, ib + 1):
+            a, b = part_begin(c, T, G), part_begin(c + 1, T, G)
+            covered += max(0, min(b, (h + 1) * nch) - max(a, h * nch))
+        assert covered == nch

@@ -1,0 +1,91 @@
+"""CPU checks of the oracle: against transformers' GPTNeoXLayer (the implementation
+the reference's end-to-end scripts compare with) and against the committed
+golden vectors."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+import make_golden as G  # noqa: E402
+from oracle import pythia_oracle as O  # noqa: E402
+
+
+@pytest.mark.parametrize("seq", [0, 5])
+def test_oracle_matches_hf_layer_small(seq):
+    """Same math as GPTNeoXLayer in fp32 (tanh GELU, rotary_pct 0.25, parallel residual)."""
+    s = G.MINI
+    w = O.make_layer_weights(s, 0, seed=5, std=0.05)
+    x = O.seeded_normal((1, s.hidden), 6)
+    k, v = O.make_kv_cache(s, seq, seq + 2, 7)
+    cos, sin = O.rope_table(seq + 1, s.rotary)
+    out, kn, vn = O.layer_decode_fp32(s, x, w, k, v, cos[seq], sin[seq], seq)
+    ho, hk, hv = O.hf_layer_decode(s, x, w, k, v, seq, seq)
+    for a, b in ((out, ho), (kn, hk), (vn, hv)):
+        assert O.compare(a, b)[0] < 2e-5
+
+
+def test_oracle_matches_hf_layer_2b8():
+    s = O.PYTHIA_2B8
+    s_, w, x, k, v, cos, sin = G.layer_case_inputs("2b8", 33, 1234, 7)
+    out, kn, vn = O.layer_decode_fp32(s, x, w, k, v, cos, sin, 33)
+    ho, hk, hv = O.hf_layer_decode(s, x, w, k, v, 33, 33)
+    for a, b in ((out, ho), (kn, hk), (vn, hv)):
+        assert O.compare(a, b)[0] < 2e-5
+
+
+@pytest.mark.parametrize("case", [c for c in G.LAYER_CASES if c[1] == "2b8"], ids=lambda c: c[0])
+def test_oracle_reproduces_golden(case):
+    name, model, seq, wseed, xseed = case
+    gold = np.load(os.path.join(HERE, "golden", name + ".npz"))
+    s, w, x, k, v, cos, sin = G.layer_case_inputs(model, seq, wseed, xseed)
+    np.testing.assert_allclose(G.checksum(x, w["qkv_weight"], w["mlp_down_weight"], k, v), gold["in_checksum"],
+                               rtol=1e-9, err_msg="seeded inputs differ from the ones the golden file was made from")
+    out, kn, vn = O.layer_decode_fp32(s, x, w, k, v, cos, sin, seq)
+    np.testing.assert_allclose(out.numpy(), gold["out"], atol=2e-5)
+    np.testing.assert_allclose(kn.numpy(), gold["k_new"], atol=2e-5)
+    np.testing.assert_allclose(vn.numpy(), gold["v_new"], atol=2e-5)
+    assert float(gold["hf_maxdiff"]) < 2e-5
+
+
+def test_mini_rollout_golden():
+    gold = np.load(os.path.join(HERE, "golden", "mini_rollout.npz"))
+    prompt, tokens, gaps, logits = G.mini_rollout_oracle(round_io=False)
+    assert prompt == gold["prompt"].tolist()
+    assert tokens == gold["tokens"].tolist()
+    assert min(gaps) > 0.01
+    np.testing.assert_allclose(logits.numpy(), gold["last_logits"], atol=1e-4)
+
+
+def test_rope_is_rotate_half_on_first_dims():
+    """cos = 1, sin = 0 leaves q untouched; dims >= rotary always pass through
+    (partial RoPE, include/5090/pythia_6b9/kernel.cuh:388-415 of the reference)."""
+    t = torch.randn(4, 128)
+    R = 32
+    ident = O.rope_partial(t, torch.ones(R), torch.zeros(R), R)
+    assert torch.equal(ident, t)
+    ang = torch.rand(R)
+    r = O.rope_partial(t, ang.cos(), ang.sin(), R)
+    assert torch.equal(r[:, R:], t[:, R:])
+    i = 3
+    expect = t[:, i] * ang.cos()[i] - t[:, i + R // 2] * ang.sin()[i]
+    assert torch.allclose(r[:, i], expect, atol=1e-6)
+    expect2 = t[:, i + R // 2] * ang.cos()[i + R // 2] + t[:, i] * ang.sin()[i + R // 2]
+    assert torch.allclose(r[:, i + R // 2], expect2, atol=1e-6)
+
+
+def test_oracle_model_step_equals_layer_composition():
+    s = G.MINI
+    layers, head = G.mini_model()
+    om = O.OracleModel(s, layers, head, 8, round_io=False)
+    logits, hid = om.step(11)
+    x = head["embed_in"][11].float().reshape(1, -1)
+    cos, sin = O.rope_table(8, s.rotary)
+    for w in layers:
+        x, _, _ = O.layer_decode_fp32(s, x, w, torch.zeros(8, s.heads * s.head_dim), torch.zeros(8, s.heads * s.head_dim),
+                                      cos[0], sin[0], 0)
+    assert torch.allclose(hid, x, atol=1e-6)
+    assert torch.allclose(logits, O.final_logits_fp32(x, head).reshape(-1), atol=1e-6)
