@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the fused Pythia decode path: per-token latency (TPOT) of greedy decode.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one generated token: embedding -> 32 fused decoder layers -> final
+LayerNorm -> LM head -> argmax.  Default workload: Pythia-6.9B shapes, seeded
+random-init fp16 weights, batch 1, 4096 cached positions, CUDA-graph replay.
+With N > 1 (launched one rank per GPU by torch.distributed.run) the weights are
+sharded by attention heads / MLP columns and each layer does one fp16 all-reduce.
+
+One JSON line is printed by rank 0.  `value` is device time per token with all
+inputs resident in HBM; `e2e` is the same loop driven through the public API with
+the token id crossing the host every step (pinned host buffers, copies inside the
+timed region).  `--impl reference` times the fp32 CPU oracle (the PyTorch forward
+the reference checks itself against) on the host cores, on a bounded sample of
+the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Pythia-6.9B B=1 decode TPOT (us) at 4K context"
+FALLBACK_HBM_GBS = 6650.0
+
+SHAPES = {  # hidden, heads, head_dim, rotary, ffn, vocab
+    "6b9": (4096, 32, 128, 32, 16384, 50432),
+    "2b8": (2560, 32, 80, 20, 10240, 50304),
+}
+
+# DRAM traffic of ONE whole-token launch (6.9B, 4096 cached rows), from ncu captures of 2- and
+# 4-layer models of the same shapes scaled to 32 layers (dram__bytes_read.sum +
+# dram__bytes_write.sum; see profiles/).  None until measured.
+NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = None
+
+
+def algorithmic_bytes_per_token(model: str, n_layers: int, ctx: float, tp: int = 1) -> float:
+    """Every weight and KV byte once, fp16; small vectors included; per GPU when tp > 1."""
+    H, NH, D, R, F, V = SHAPES[model]
+    per_layer = (2 * (3 * H * H + H * H + 2 * H * F) / tp          # QKV, dense, up, down weights
+                 + 2 * (3 * H + F) / tp + 2 * (H + H + 4 * H)      # biases (sharded / replicated), LN params
+                 + 2 * 2 * ctx * H / tp                            # K and V history
+                 + 2 * 2 * H / tp + 2 * 2 * H)                     # K/V append, hidden in + out
+    return n_layers * per_layer + 2 * V * H / tp + 2 * H + 2 * 2 * H
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.samples, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
+
+    def summary(self, t0: float, t1: float) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+        rows = [r for t, r in self.samples if t0 <= t <= t1] or [r for _, r in self.samples[-3:]]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "").isdigit() else None,
+                "power_w_max": max((float(r[2]) for r in rows if r[2].replace(".", "").isdigit()), default=None),
+                "samples": len(rows), "reasons": reasons}
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json copy bandwidth)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------ CPU oracle arm
+def oracle_tpot_us(model: str, n_layers: int, ctx: int, sample_layers: int, reps: int, warmup: int):
+    """fp32 PyTorch forward on the host cores: `sample_layers` layers + the LM head, scaled to n_layers."""
+    from oracle import pythia_oracle as O
+    s = O.SHAPES[model]
+    torch.set_num_threads(os.cpu_count() or 1)
+    layers = [{k: v.float() for k, v in O.make_layer_weights(s, l, seed=1).items()} for l in range(sample_layers)]
+    head = {k: v.float() for k, v in O.make_head_weights(s, seed=1).items()}
+    caches = [tuple(c.float() for c in O.make_kv_cache(s, ctx, ctx + 1, 50 + l)) for l in range(sample_layers)]
+    cos, sin = O.rope_table(ctx + 1, s.rotary)
+    x0 = head["embed_in"][17].reshape(1, -1)
+    times = []
+    for it in range(warmup + reps):
+        t0 = time.perf_counter()
+        x = x0
+        for l in range(sample_layers):
+            x, _, _ = O.layer_decode_fp32(s, x, layers[l], caches[l][0], caches[l][1], cos[ctx], sin[ctx], ctx)
+        t1 = time.perf_counter()
+        logits = O.final_logits_fp32(x, head)
+        int(logits.argmax())
+        t2 = time.perf_counter()
+        if it >= warmup:
+            times.append(((t1 - t0) / sample_layers * n_layers + (t2 - t1)) * 1e6)
+    return times, torch.get_num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    t_start = time.perf_counter()
+    times, cores = oracle_tpot_us(args.model, args.layers, args.ctx, args.sample_layers, args.steps, args.warmup)
+    us = statistics.mean(times)
+    sample = (f"{args.sample_layers} of {args.layers} layers + LM head per step, fp32 torch on CPU, "
+              f"layer time scaled x{args.layers / args.sample_layers:g}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us/token", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, 1),
+        "cpu_baseline": {"value": us, "unit": "us/token", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": us, "unit": "us/token", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_start,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, tp):
+    return {"workload": f"pythia-{args.model} greedy decode, batch 1, {args.layers} layers, {args.ctx} cached positions, "
+                        f"one token per step, CUDA graph replay",
+            "context": args.ctx, "layers": args.layers, "parallelism": f"tp{tp}" if tp > 1 else "single",
+            "l2": "inputs larger than L2 (weights + KV read once per token: GBs vs 126 MB)"}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def rand_half(shape, gen, dev, mean=0.0, std=0.02):
+    return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std + mean).half()
+
+
+def build_model(args, dev, rank, tp):
+    """Seeded random-init tensors straight on the GPU.  Replicated tensors use the same seed on
+    every rank, sharded ones a rank-specific seed (any N(0, 0.02) shard is as good as another)."""
+    H, NH, D, R, F, V = SHAPES[args.model]
+    g_rep = torch.Generator(device=dev)
+    g_rep.manual_seed(1234)
+    g_loc = torch.Generator(device=dev)
+    g_loc.manual_seed(999 + rank)
+    nh, f, v = NH // tp, F // tp, V // tp
+    kvw = nh * D
+    layers, caches = [], []
+    max_seq = args.ctx + args.steps + args.warmup + 2 * 8 + 8
+    for _ in range(args.layers):
+        layers.append({
+            "qkv_weight": rand_half((3 * kvw, H), g_loc, dev), "qkv_bias": rand_half((3 * kvw,), g_loc, dev),
+            "o_weight": rand_half((H, kvw), g_loc, dev), "o_bias": rand_half((H,), g_rep, dev),
+            "ln_weight": rand_half((H,), g_rep, dev, 1.0), "ln_bias": rand_half((H,), g_rep, dev),
+            "post_ln_weight": rand_half((H,), g_rep, dev, 1.0), "post_ln_bias": rand_half((H,), g_rep, dev),
+            "mlp_up_weight": rand_half((f, H), g_loc, dev), "mlp_up_bias": rand_half((f,), g_loc, dev),
+            "mlp_down_weight": rand_half((H, f), g_loc, dev), "mlp_down_bias": rand_half((H,), g_rep, dev),
+        })
+        k = torch.zeros(max_seq, kvw, dtype=torch.float16, device=dev)
+        vv = torch.zeros(max_seq, kvw, dtype=torch.float16, device=dev)
+        k[:args.ctx] = rand_half((args.ctx, kvw), g_loc, dev, std=1.0)
+        vv[:args.ctx] = rand_half((args.ctx, kvw), g_loc, dev, std=1.0)
+        caches.append((k, vv))
+    head = {"embed_in": rand_half((V, H), g_rep, dev), "final_ln_weight": rand_half((H,), g_rep, dev, 1.0),
+            "final_ln_bias": rand_half((H,), g_rep, dev), "embed_out": rand_half((v, H), g_loc, dev)}
+    return layers, head, caches, max_seq
+
+
+def run_ours(args, rank, world):
+    import torch.distributed as dist
+    import clusterfusionplus_b200 as cf
+
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tp = world
+    if tp > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    H, NH, D, R, F, V = SHAPES[args.model]
+    dims = cf.CfDims()
+    dims.hidden, dims.heads, dims.head_dim, dims.rotary, dims.ffn, dims.vocab = H, NH, D, R, F, V
+    layers, head, caches, max_seq = build_model(args, dev, rank, tp)
+    if tp == 1:
+        dec = cf.PythiaDecoder(dims, layers, head, caches, max_seq, use_graph=True)
+        launches_per_token = 1
+    else:
+        dec = cf.TPDecoder(dims, layers, head, caches, max_seq, use_graph=True)
+        launches_per_token = dec.launches_per_token
+    K, W = args.steps, args.warmup
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: device time, everything resident
+    dec.reset(args.ctx, 17)
+    for _ in range(W):
+        dec.step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(K):
+        dec.step()
+    e1.record()
+    barrier()
+    t1 = time.perf_counter()
+    ms = e0.elapsed_time(e1)
+    status = cf.device_status()
+    if tp > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    clocks = sampler.summary(t0, t1) if sampler else None
+    tpot_us = ms / K * 1e3
+    mean_ctx = args.ctx + W + K / 2
+
+    # ---- e2e: token id crosses the host every step (pinned buffers), copies timed
+    pin_in = torch.zeros(1, dtype=torch.int32).pin_memory()
+    pin_out = torch.zeros(1, dtype=torch.int32).pin_memory()
+    dec.reset(args.ctx, 17)
+    pin_in[0] = 17
+    for _ in range(W):
+        dec.token.copy_(pin_in, non_blocking=True)
+        dec.step()
+        pin_out.copy_(dec.token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        pin_in[0] = int(pin_out[0])
+    barrier()
+    e0.record()
+    w0 = time.perf_counter()
+    for _ in range(K):
+        dec.token.copy_(pin_in, non_blocking=True)
+        dec.step()
+        pin_out.copy_(dec.token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        pin_in[0] = int(pin_out[0])
+    e1.record()
+    barrier()
+    w1 = time.perf_counter()
+    e2e_ms = max(e0.elapsed_time(e1), (w1 - w0) * 1e3)
+    if tp > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    status = status or cf.device_status()
+    if rank != 0:
+        dec.close()
+        if tp > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = hbm_peak()
+    bytes_token = algorithmic_bytes_per_token(args.model, args.layers, mean_ctx, tp)
+    achieved = bytes_token / (tpot_us * 1e-6) / 1e9
+    traffic = None
+    if tp == 1 and args.model == "6b9" and args.ctx == 4096 and args.layers == 32:
+        traffic = NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K
+    line = {
+        "metric": METRIC, "value": tpot_us, "unit": "us/token", "n_gpus": tp, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp16 (fp32 accumulate)", "data": "synthetic", "config": workload_config(args, tp),
+        "clocks": clocks,
+        "e2e": {"value": e2e_ms / K * 1e3, "unit": "us/token", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+        "gpu_launches": K * launches_per_token,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_source": peak_src, "bytes_per_launch_algorithmic": bytes_token,
+                     "frac_of_8TBs_nominal": achieved / 8000.0, "per_gpu": tp > 1,
+                     "kernel": "fused_decode_kernel (one launch per token)" if tp == 1 else
+                               "fused_decode_kernel per layer + NCCL all-reduce (whole token timed)"},
+        "launch": cf.launch_info(cf.CF_PYTHIA_6B9 if args.model == "6b9" else cf.CF_PYTHIA_2B8),
+        "device_status": status,
+    }
+    if tp == 1 and not args.no_cpu_baseline:
+        times, cores = oracle_tpot_us(args.model, args.layers, args.ctx, args.sample_layers, 5, 1)
+        line["cpu_baseline"] = {
+            "value": statistics.mean(times), "unit": "us/token", "cores": cores, "kind": "port",
+            "sample": f"{args.sample_layers} of {args.layers} layers + LM head, 5 steps after 1 warm-up, fp32 torch oracle, "
+                      f"layer time scaled x{args.layers / args.sample_layers:g}"}
+    print(json.dumps(line), flush=True)
+    dec.close()
+    if tp > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="6b9", choices=sorted(SHAPES))
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--sample-layers", type=int, default=2, help="layers the CPU oracle runs per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 "
+                             "--nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...")
+    run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -172,12 +172,17 @@ def gelu_tanh(x):
 def layer_decode_fp32(shape: Shape, x: torch.Tensor, w: Dict[str, torch.Tensor],
                       k_cache: torch.Tensor, v_cache: torch.Tensor,
                       cos: torch.Tensor, sin: torch.Tensor, seq_len: int,
-                      intermediates: Optional[dict] = None):
+                      intermediates: Optional[dict] = None, partial: bool = False):
     """One decode step of one layer in fp32.
 
     x [1,H]; caches [rows, NH*D] of which rows [0, seq_len) are history (not
     modified here); cos/sin fp32, first R entries used.
     Returns (out [1,H], k_new [1,NH,D], v_new [1,NH,D]) in fp32.
+
+    `shape.heads` / `shape.ffn` may describe a tensor-parallel shard (fewer heads,
+    narrower MLP, full hidden width).  With partial=True the result is the shard's
+    contribution attn @ Wo^T + mid @ Wdown^T only: no residual, no dense / down bias
+    (those are added once, after the partials of all shards are summed).
     """
     H, NH, D, R = shape.hidden, shape.heads, shape.head_dim, shape.rotary
     f = lambda t: t.detach().to("cpu", torch.float32)
@@ -200,12 +205,14 @@ def layer_decode_fp32(shape: Shape, x: torch.Tensor, w: Dict[str, torch.Tensor],
     v_all = torch.cat([v_hist, v_new[None]], dim=0).transpose(0, 1)
     scores = torch.einsum("hd,hsd->hs", q, k_all) / math.sqrt(D)
     p = torch.softmax(scores, dim=-1)
-    attn = torch.einsum("hs,hsd->hd", p, v_all).reshape(1, H)
+    attn = torch.einsum("hs,hsd->hd", p, v_all).reshape(1, NH * D)
 
     attn_out = attn @ W["o_weight"].t() + W["o_bias"]
     mid = gelu_tanh(y2 @ W["mlp_up_weight"].t() + W["mlp_up_bias"])
     mlp_out = mid @ W["mlp_down_weight"].t() + W["mlp_down_bias"]
     out = x + attn_out + mlp_out
+    if partial:
+        out = attn @ W["o_weight"].t() + mid @ W["mlp_down_weight"].t()
     if intermediates is not None:
         intermediates.update(y1=y1, y2=y2, q=q, attn=attn, attn_out=attn_out, mid=mid,
                              mlp_out=mlp_out)
