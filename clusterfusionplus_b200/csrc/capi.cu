@@ -552,6 +552,80 @@ void decoder_params(Decoder& dc, Params& p) {
     p.hid[1] = dc.hid1;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch for cf_pythia_decoder_layer_noalloc: everything the fused layer kernel
+// needs beyond its inputs and outputs, in one statically allocated device array.
+// Sized for the two built-in models on a grid of at most NOALLOC_MAX_GRID CTAs.
+// Every GPU that loads this library holds these bytes until the process exits.
+constexpr int NOALLOC_MAX_GRID = 160;
+constexpr int NOALLOC_MAX_HEADS = 32;
+constexpr int NOALLOC_MAX_KVW = 4096;   // heads * head_dim
+constexpr int NOALLOC_MAX_FFN = 16384;
+constexpr size_t NA_OFF_QKV = 0;
+constexpr size_t NA_OFF_MID = NA_OFF_QKV + sizeof(float) * 3 * NOALLOC_MAX_KVW;
+constexpr size_t NA_OFF_PART = NA_OFF_MID + sizeof(float) * NOALLOC_MAX_FFN;
+constexpr size_t NA_OFF_NEW = NA_OFF_PART + sizeof(float) * NOALLOC_MAX_GRID * MAXL * (128 + 2);
+constexpr size_t NA_OFF_AMAXV = NA_OFF_NEW + sizeof(float) * NOALLOC_MAX_HEADS * (128 + 2);
+constexpr size_t NA_OFF_AMAXI = NA_OFF_AMAXV + sizeof(float) * NOALLOC_MAX_GRID;
+constexpr size_t NA_OFF_SYNC = NA_OFF_AMAXI + sizeof(int) * NOALLOC_MAX_GRID;   // 4 barrier words + 4 status words
+constexpr size_t NA_OFF_DESC = (NA_OFF_SYNC + 32 + 255) / 256 * 256;            // one LayerDesc (tensor maps)
+constexpr size_t NOALLOC_SCRATCH_BYTES = NA_OFF_DESC + sizeof(LayerDesc);
+static_assert(NOALLOC_SCRATCH_BYTES <= 512 * 1024, "the static scratch is meant to stay modest");
+static_assert(NA_OFF_MID % 256 == 0 && NA_OFF_PART % 256 == 0 && NA_OFF_NEW % 128 == 0 && NA_OFF_SYNC % 16 == 0,
+              "sub-buffers must keep the alignment the kernel's vector loads and tensor maps need");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // DEVICE address of g_noalloc_scratch on this GPU
+    DeviceState ds;                    // launch geometry only; its workspace points into the scratch
+    DescKey last_key;                  // what the descriptor slot currently holds
+    bool have_key = false;
+};
+NoAllocDevice g_noalloc[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current.  In host code the array's name is only
+// a stand-in, not a device address: the address has to be asked for.
+int noalloc_setup(NoAllocDevice** out) {
+    int dev = -1;
+    CF_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(CF_ERR_UNSUPPORTED, "device index %d", dev);
+    NoAllocDevice& nd = g_noalloc[dev];
+    if (!nd.ready) {
+        cudaDeviceProp prop;
+        CF_CUDA(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10)
+            return fail(CF_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                        prop.major, prop.minor);
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(CF_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        nd.scratch = static_cast<unsigned char*>(ptr);
+        nd.ds.dev = dev;
+        nd.ds.sm_count = prop.multiProcessorCount;
+        int optin = 0;
+        CF_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        nd.ds.smem_optin = optin;
+        Workspace& w = nd.ds.ws;
+        w.base = nd.scratch;
+        w.qkv_f32 = reinterpret_cast<float*>(nd.scratch + NA_OFF_QKV);
+        w.mid_f32 = reinterpret_cast<float*>(nd.scratch + NA_OFF_MID);
+        w.attn_part = reinterpret_cast<float*>(nd.scratch + NA_OFF_PART);
+        w.attn_new = reinterpret_cast<float*>(nd.scratch + NA_OFF_NEW);
+        w.amax_val = reinterpret_cast<float*>(nd.scratch + NA_OFF_AMAXV);
+        w.amax_idx = reinterpret_cast<int*>(nd.scratch + NA_OFF_AMAXI);
+        w.sync = reinterpret_cast<unsigned*>(nd.scratch + NA_OFF_SYNC);
+        w.status = reinterpret_cast<int*>(nd.scratch + NA_OFF_SYNC + 16);
+        nd.ready = true;
+    }
+    *out = &nd;
+    return CF_OK;
+}
+
 }  // namespace
 
 // =============================================================================
@@ -617,6 +691,59 @@ int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO*
 int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
                                   void* stream) {
     return run_layer(model, w, io, seq_len, stream, true);
+}
+
+int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
+                                    void* stream) {
+    CfDims d;
+    int rc = model_dims(model, &d);
+    if (rc) return rc;
+    if ((rc = check_layer_args(w, io, seq_len, true, true))) return rc;
+    if (d.heads > NOALLOC_MAX_HEADS || d.heads * d.head_dim > NOALLOC_MAX_KVW || d.ffn > NOALLOC_MAX_FFN)
+        return fail(CF_ERR_UNSUPPORTED,
+                    "model too large for the static scratch (%zu bytes: at most %d heads, %d QKV columns, ffn %d)",
+                    NOALLOC_SCRATCH_BYTES, NOALLOC_MAX_HEADS, NOALLOC_MAX_KVW, NOALLOC_MAX_FFN);
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocDevice* nd;
+    if ((rc = noalloc_setup(&nd))) return rc;
+    if ((rc = pick_cfg(nd->ds, d.head_dim))) return rc;
+    if (nd->ds.cfg[d.head_dim == 128].grid > NOALLOC_MAX_GRID)
+        return fail(CF_ERR_UNSUPPORTED, "this GPU runs %d CTAs; the static scratch holds partials for at most %d",
+                    nd->ds.cfg[d.head_dim == 128].grid, NOALLOC_MAX_GRID);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the last call left: barrier and status words must start at zero
+    CF_CUDA(cudaMemsetAsync(nd->ds.ws.sync, 0, 32, st));
+    // tensor maps + pointers of this call's tensors into the descriptor slot (a copy, not an allocation)
+    DescKey key;
+    memset(&key, 0, sizeof(key));
+    const void* ptrs[14] = {w->qkv_weight, w->qkv_bias, w->o_weight, w->o_bias, w->ln_weight, w->ln_bias,
+                            w->post_ln_weight, w->post_ln_bias, w->mlp_up_weight, w->mlp_up_bias, w->mlp_down_weight,
+                            w->mlp_down_bias, io->k_cache, io->v_cache};
+    memcpy(key.p, ptrs, sizeof(ptrs));
+    key.kv_rows = io->kv_rows;
+    key.dims[0] = d.hidden; key.dims[1] = d.heads; key.dims[2] = d.head_dim; key.dims[3] = d.ffn; key.dims[4] = d.rotary;
+    LayerDesc* desc = reinterpret_cast<LayerDesc*>(nd->scratch + NA_OFF_DESC);
+    if (!nd->have_key || memcmp(&key, &nd->last_key, sizeof(key)) != 0) {
+        LayerDesc host;
+        if ((rc = build_layer_desc(host, d, *w, io->k_cache, io->v_cache, io->kv_rows))) return rc;
+        CF_CUDA(cudaMemcpyAsync(desc, &host, sizeof(LayerDesc), cudaMemcpyHostToDevice, st));
+        nd->last_key = key;
+        nd->have_key = true;
+    }
+    Params p;
+    base_params(p, d, nd->ds.ws);
+    p.layers = desc;
+    p.n_layers = 1;
+    p.p3_flags = F3_FULL;
+    p.phase_mask = PH_P1 | PH_P2 | PH_P3;
+    p.x_in = static_cast<const __half*>(io->input);
+    p.out = static_cast<__half*>(io->output);
+    p.k_new = static_cast<__half*>(io->k_new);
+    p.v_new = static_cast<__half*>(io->v_new);
+    p.cos = io->cos;
+    p.sin = io->sin;
+    p.seq_host = static_cast<int>(seq_len);
+    return launch(nd->ds, d, p, st);
 }
 
 int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, int phase_mask,

@@ -98,6 +98,28 @@ int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO*
 int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
                                   void* stream);
 
+/* The fused decoder layer for callers that cannot allocate device memory at the point
+ * of the call: code running under a memory pool that owns the whole GPU (inference
+ * servers that pre-reserve all of HBM, so a late cudaMalloc fails or fragments), and
+ * callers inside a region where allocation is forbidden (e.g. they already hold the
+ * allocator's lock).  Same arguments, same result bits as cf_pythia_decoder_layer, but
+ * this entry point performs no cudaMalloc / cudaFree and calls no allocating routine:
+ * its scratch (fp32 QKV and MLP intermediates, attention partials, barrier words and
+ * the layer descriptor with its tensor maps) lives in a static __device__ array of
+ * 466,560 bytes that every GPU loading the library holds until exit.
+ *   Limits: the built-in models only (at most 32 heads, 4096 QKV columns, ffn 16384)
+ *   on at most 160 CTAs; anything larger is rejected with CF_ERR_UNSUPPORTED.
+ *   The first call on a device looks up the array's device address and the launch
+ *   geometry; make that first call outside any stream capture.
+ *   All calls on a device share the one array and it keeps the previous call's
+ *   contents (the words that must start at zero are cleared on `stream` each call):
+ *   two calls whose kernels overlap on the GPU (different streams) race.
+ *   Device-side status of these launches is not part of cf_get_status.
+ * No counterpart in the reference (its dispatcher allocates five tensors per call:
+ * include/5090/pythia_6b9/pythia_kernel_dispatch.cu:31-39). */
+int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
+                                    void* stream);
+
 /* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
  * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one
  * launch, reading what earlier phases left in the library's scratch.  Used by the
