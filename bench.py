@@ -42,8 +42,8 @@ SHAPES = {  # hidden, heads, head_dim, rotary, ffn, vocab
 
 # DRAM traffic of ONE whole-token launch (6.9B, 4096 cached rows), from ncu captures of 2- and
 # 4-layer models of the same shapes scaled to 32 layers (dram__bytes_read.sum +
-# dram__bytes_write.sum; see profiles/).  None until measured.
-NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = None
+# dram__bytes_write.sum).
+NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = 15.551e9  # 417.9 MB tail + 32 x 472.9 MB (profiles/decoder_6b9_ctx4096_traffic.md)
 
 
 def algorithmic_bytes_per_token(model: str, n_layers: int, ctx: float, tp: int = 1) -> float:
@@ -66,7 +66,7 @@ class ClockSampler:
         self.samples, self.proc = [], None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -226,11 +226,13 @@ def run_ours(args, rank, world):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
+    torch.cuda.nvtx.range_push("value_timed")
     e0.record()
     for _ in range(K):
         dec.step()
     e1.record()
     barrier()
+    torch.cuda.nvtx.range_pop()
     t1 = time.perf_counter()
     ms = e0.elapsed_time(e1)
     status = cf.device_status()
