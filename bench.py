@@ -151,7 +151,8 @@ def run_reference(args, rank):
 def workload_config(args, tp):
     return {"workload": f"pythia-{args.model} greedy decode, batch 1, {args.layers} layers, {args.ctx} cached positions, "
                         f"one token per step, CUDA graph replay",
-            "context": args.ctx, "layers": args.layers, "parallelism": f"tp{tp}" if tp > 1 else "single",
+            "context": args.ctx, "layers": args.layers,
+            "parallelism": (f"tp{tp} ({args.tp_mode} all-reduce)" if tp > 1 else "single"),
             "l2": "inputs larger than L2 (weights + KV read once per token: GBs vs 126 MB)"}
 
 
@@ -209,7 +210,7 @@ def run_ours(args, rank, world):
         dec = cf.PythiaDecoder(dims, layers, head, caches, max_seq, use_graph=True)
         launches_per_token = 1
     else:
-        dec = cf.TPDecoder(dims, layers, head, caches, max_seq, use_graph=True)
+        dec = cf.TPDecoder(dims, layers, head, caches, max_seq, use_graph=True, fused=(args.tp_mode == "fused"))
         launches_per_token = dec.launches_per_token
     K, W = args.steps, args.warmup
 
@@ -295,7 +296,7 @@ def run_ours(args, rank, world):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_source": peak_src, "bytes_per_launch_algorithmic": bytes_token,
                      "frac_of_8TBs_nominal": achieved / 8000.0, "per_gpu": tp > 1,
-                     "kernel": "fused_decode_kernel (one launch per token)" if tp == 1 else
+                     "kernel": "fused_decode_kernel (one launch per token)" if (tp == 1 or args.tp_mode == "fused") else
                                "fused_decode_kernel per layer + NCCL all-reduce (whole token timed)"},
         "launch": cf.launch_info(cf.CF_PYTHIA_6B9 if args.model == "6b9" else cf.CF_PYTHIA_2B8),
         "device_status": status,
@@ -323,6 +324,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--sample-layers", type=int, default=2, help="layers the CPU oracle runs per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: in-kernel all-reduce over peer memory (default) or one NCCL all-reduce per layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", 0))

@@ -73,6 +73,8 @@ SIGNATURES = {
     "cf_decoder_set_head": (C.c_int, [C.c_int64, _P(CfHeadWeights)]),
     "cf_decoder_finalize": (C.c_int, [C.c_int64]),
     "cf_decoder_state": (C.c_int, [C.c_int64] + [_P(C.c_void_p)] * 7),
+    "cf_decoder_tp_export": (C.c_int, [C.c_int64, C.c_void_p]),
+    "cf_decoder_tp_connect": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_step": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_layer_partial": (C.c_int, [C.c_int64, C.c_int, C.c_void_p]),
     "cf_decoder_layer_finish": (C.c_int, [C.c_int64, C.c_int, C.c_void_p]),

@@ -110,8 +110,8 @@ int ws_alloc(Workspace& w) {
     };
     const size_t o_qkv = take(sizeof(float) * WS_MAX_QKV);
     const size_t o_mid = take(sizeof(float) * WS_MAX_F);
-    const size_t o_part = take(sizeof(float) * WS_MAX_GRID * MAXL * (128 + 2));
-    const size_t o_new = take(sizeof(float) * WS_MAX_HEADS * (128 + 2));
+    const size_t o_part = take(sizeof(float) * WS_MAX_GRID * MAXL * (128 + 4));
+    const size_t o_new = take(sizeof(float) * WS_MAX_HEADS * (128 + 4));
     const size_t o_av = take(sizeof(float) * WS_MAX_GRID);
     const size_t o_ai = take(sizeof(int) * WS_MAX_GRID);
     const size_t o_sync = take(sizeof(unsigned) * 4);
@@ -529,6 +529,11 @@ struct Decoder {
     int *token_d = nullptr, *seq_d = nullptr;
     float* logits_d = nullptr;
     __half *hidden_d = nullptr, *hid0 = nullptr, *hid1 = nullptr, *partial_d = nullptr;
+    // fused tensor-parallel exchange (peer memory over NVLink)
+    unsigned char* tp_local = nullptr;          // this rank's exchange buffer (cudaMalloc, exported by IPC)
+    unsigned char* tp_peer[MAX_TP] = {nullptr};  // every rank's buffer as mapped here ([tp_rank] == tp_local)
+    unsigned* tp_count = nullptr;
+    bool tp_connected = false;
 };
 
 std::unordered_map<int64_t, Decoder*> g_decoders;
@@ -564,8 +569,8 @@ constexpr int NOALLOC_MAX_FFN = 16384;
 constexpr size_t NA_OFF_QKV = 0;
 constexpr size_t NA_OFF_MID = NA_OFF_QKV + sizeof(float) * 3 * NOALLOC_MAX_KVW;
 constexpr size_t NA_OFF_PART = NA_OFF_MID + sizeof(float) * NOALLOC_MAX_FFN;
-constexpr size_t NA_OFF_NEW = NA_OFF_PART + sizeof(float) * NOALLOC_MAX_GRID * MAXL * (128 + 2);
-constexpr size_t NA_OFF_AMAXV = NA_OFF_NEW + sizeof(float) * NOALLOC_MAX_HEADS * (128 + 2);
+constexpr size_t NA_OFF_NEW = NA_OFF_PART + sizeof(float) * NOALLOC_MAX_GRID * MAXL * (128 + 4);
+constexpr size_t NA_OFF_AMAXV = NA_OFF_NEW + sizeof(float) * NOALLOC_MAX_HEADS * (128 + 4);
 constexpr size_t NA_OFF_AMAXI = NA_OFF_AMAXV + sizeof(float) * NOALLOC_MAX_GRID;
 constexpr size_t NA_OFF_SYNC = NA_OFF_AMAXI + sizeof(int) * NOALLOC_MAX_GRID;   // 4 barrier words + 4 status words
 constexpr size_t NA_OFF_DESC = (NA_OFF_SYNC + 32 + 255) / 256 * 256;            // one LayerDesc (tensor maps)
@@ -1110,16 +1115,71 @@ int cf_decoder_state(int64_t handle, int** token, int** seq_len, float** logits,
     return CF_OK;
 }
 
+int cf_decoder_tp_export(int64_t handle, void* ipc_handle_out) {
+    Decoder* dc;
+    int rc = find_decoder(handle, &dc);
+    if (rc) return rc;
+    if (!ipc_handle_out) return fail(CF_ERR_INVALID, "null handle buffer");
+    if (dc->cfg.tp_size < 2 || dc->cfg.tp_size > MAX_TP) return fail(CF_ERR_INVALID, "tp_size %d (2..%d)", dc->cfg.tp_size, MAX_TP);
+    DeviceState* ds;
+    if ((rc = get_device(&ds))) return rc;
+    if ((rc = pick_cfg(*ds, dc->cfg.dims.head_dim))) return rc;
+    if (!dc->tp_local) {
+        const TpLayout tl{dc->cfg.dims.hidden, dc->cfg.tp_size};  // zero-filled: epoch 0 means never written
+        const size_t bytes = align_up(tl.bytes(), 256) + 256;
+        CF_CUDA(cudaMalloc(&dc->tp_local, bytes));
+        CF_CUDA(cudaMemset(dc->tp_local, 0, bytes));
+        dc->tp_count = reinterpret_cast<unsigned*>(dc->tp_local + align_up(tl.bytes(), 256));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CF_CUDA(cudaIpcGetMemHandle(&h, dc->tp_local));
+    memcpy(ipc_handle_out, &h, sizeof(h));
+    return CF_OK;
+}
+
+int cf_decoder_tp_connect(int64_t handle, const void* all_handles) {
+    Decoder* dc;
+    int rc = find_decoder(handle, &dc);
+    if (rc) return rc;
+    if (!all_handles) return fail(CF_ERR_INVALID, "null handles");
+    if (!dc->tp_local) return fail(CF_ERR_INVALID, "call cf_decoder_tp_export first");
+    if (dc->tp_connected) return CF_OK;
+    for (int r = 0; r < dc->cfg.tp_size; ++r) {
+        if (r == dc->cfg.tp_rank) {
+            dc->tp_peer[r] = dc->tp_local;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const char*>(all_handles) + 64 * r, sizeof(h));
+        void* ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess)
+            return fail(CF_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d failed: %s (peer access over NVLink is required)", r,
+                        cudaGetErrorString(e));
+        dc->tp_peer[r] = static_cast<unsigned char*>(ptr);
+    }
+    dc->tp_connected = true;
+    return CF_OK;
+}
+
 int cf_decoder_step(int64_t handle, void* stream) {
     Decoder* dc;
     int rc = find_decoder(handle, &dc);
     if (rc) return rc;
     if (!dc->finalized) return fail(CF_ERR_INVALID, "decoder not finalized");
-    if (dc->cfg.tp_size != 1) return fail(CF_ERR_INVALID, "cf_decoder_step is the single-GPU path; use the layer_partial/finish/tail calls");
+    if (dc->cfg.tp_size != 1 && !dc->tp_connected)
+        return fail(CF_ERR_INVALID, "tensor-parallel decoder: exchange buffers not connected (cf_decoder_tp_export / cf_decoder_tp_connect), or use the layer_partial/finish/tail calls");
     DeviceState* ds;
     if ((rc = get_device(&ds))) return rc;
     Params p;
     decoder_params(*dc, p);
+    if (dc->cfg.tp_size > 1) {
+        p.tp_size = dc->cfg.tp_size;
+        p.tp_rank = dc->cfg.tp_rank;
+        for (int r = 0; r < dc->cfg.tp_size; ++r) p.tp_peer[r] = dc->tp_peer[r];
+        p.tp_launch_count = dc->tp_count;
+    }
     p.layers = dc->layers_d;
     p.tail = dc->tail_d;
     p.n_layers = dc->cfg.n_layers;
@@ -1214,6 +1274,9 @@ int cf_decoder_destroy(int64_t handle) {
         g_decoders.erase(it);
     }
     cudaDeviceSynchronize();
+    for (int r = 0; r < MAX_TP; ++r)
+        if (dc->tp_peer[r] && dc->tp_peer[r] != dc->tp_local) cudaIpcCloseMemHandle(dc->tp_peer[r]);
+    if (dc->tp_local) cudaFree(dc->tp_local);
     cudaFree(dc->token_d);
     cudaFree(dc->ws.base);
     delete dc;

@@ -48,13 +48,16 @@ constexpr int STAGE_BYTES = NSLOT * SLOT_BYTES;  // 36 KB
 constexpr int MAX_STAGES = 8;
 constexpr int NCWARP = 8;                   // consumer warps
 constexpr int NCTHR = NCWARP * 32;          // consumer threads
-constexpr int NTHREADS = NCTHR + 32;        // + producer warp
+constexpr int NHWARP = 3;                   // helper warps: latency-bound side work off the consumers' path
+constexpr int NHTHR = NHWARP * 32;
+constexpr int NTHREADS = NCTHR + 32 + NHTHR;  // consumers + producer warp + helpers = 12 warps (register-file granule)
 constexpr int KV_TILE = 64;                 // cache rows per attention item
 constexpr int MAXL = 4;                     // attention partial slots per CTA
 constexpr int MAX_P3_ROWS = 256;            // output rows one cluster may own in P3
 constexpr int MAX_H = 4096;                 // LayerNorm register staging limit
 constexpr int WTS_SLOTS = 640;              // (attention chunk, head, partial) merge weights one CTA may need
 constexpr int MAX_PARTS = 64;               // partials one head may be split into
+constexpr int MAX_TP = 8;                   // ranks of a tensor-parallel group
 
 enum : int { PH_P1 = 1, PH_P2 = 2, PH_P3 = 4, PH_P4 = 8 };
 enum : int {
@@ -115,8 +118,8 @@ struct Params {
     // scratch
     float* qkv_f32;    // [3*NH*D]
     float* mid_f32;    // [F]
-    float* attn_part;  // [grid][MAXL][D+2]
-    float* attn_new;   // [NH][D+2]
+    float* attn_part;  // [grid][MAXL][D+4]: D numerators, max, denominator, 2 pad
+    float* attn_new;   // [NH][D+4]
     unsigned* sync;    // [0] barrier count, [1] exit count
     int* status;
     // tail outputs
@@ -128,7 +131,39 @@ struct Params {
     int vocab_offset;  // added to the argmax index (vocabulary shards)
     // optional timeline: [grid][n_layers + 1][TRACE_EVENTS] globaltimer stamps (diagnostics)
     unsigned long long* trace;
+    // tensor-parallel exchange over peer memory (tp_size > 1): every rank owns one buffer laid
+    // out as TpLayout; tp_peer[r] is rank r's buffer as mapped into this process.
+    int tp_size, tp_rank;
+    unsigned char* tp_peer[MAX_TP];
+    unsigned* tp_launch_count;  // local word, +1 per launch: makes epochs strictly increasing
 };
+
+// Exchange buffer of one rank (H = hidden).  Every word travels with the epoch it belongs
+// to in the same aligned 8-byte store (value, epoch), so a reader that sees the epoch has the
+// value: no fence and no separate flag, one NVLink crossing of latency.
+//   partial[2][tp][H]  {fp32 value, u32 epoch}   slot [layer parity][source rank]
+//   pairs  [2][tp][2]  {bits, u32 epoch}         slot [launch parity][source rank]: max logit, index
+struct TpLayout {
+    int H, tp;
+    __host__ __device__ size_t partial_off(int parity, int src) const { return (static_cast<size_t>(parity) * tp + src) * H * 8; }
+    __host__ __device__ size_t pairs_off(int parity, int src) const { return static_cast<size_t>(2) * tp * H * 8 + (static_cast<size_t>(parity) * tp + src) * 16; }
+    __host__ __device__ size_t bytes() const { return pairs_off(2, 0); }
+};
+
+__device__ __forceinline__ void st_ll(void* p, unsigned bits, unsigned epoch) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ uint2 ld_ll(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// wait (bounded) until the word at p carries `epoch`; returns its payload bits
+__device__ __forceinline__ unsigned wait_ll(const void* p, unsigned epoch, const AbortCtl& ab) {
+    uint2 v = ld_ll(p);
+    if (v.y != epoch) wait_bounded([&] { v = ld_ll(p); return v.y == epoch; }, ab, ST_TIMEOUT_PEER);
+    return v.x;
+}
 
 constexpr int TRACE_EVENTS = 16;
 enum : int {
@@ -177,12 +212,14 @@ struct Smem {
     uint64_t* full;
     uint64_t* empty;
     uint64_t* xbar;
+    uint64_t* h_go;        // consumers -> helpers: the barrier before P3 has been passed
+    uint64_t* attn_ready;  // helpers -> consumers: merged attention chunks are in xbuf
     int* abort_flag;
 };
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 1) * 8 + 16;
+           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 3) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -200,7 +237,9 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
     s.empty = s.full + MAX_STAGES;
     s.xbar = s.empty + MAX_STAGES;
-    s.abort_flag = reinterpret_cast<int*>(s.xbar + 1);
+    s.h_go = s.xbar + 1;
+    s.attn_ready = s.xbar + 2;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 3);
     return s;
 }
 
@@ -453,8 +492,11 @@ struct Consumer {
     }
     // Mirror of Producer::rows_phase.  xs = activations in shared memory (KC*256
     // floats); epi(granule index relative to g0=0, row in granule, dot product).
+    // gate_chunk >= 0: before the first use of activation chunk `gate_chunk`, wait (bounded)
+    // on mbarrier gate_bar / gate_parity (the helpers' "chunks from here on are ready").
     template <class Epi>
-    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi) {
+    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi, int gate_chunk = -1,
+                                               uint32_t gate_bar = 0, uint32_t gate_parity = 0) {
         if (cnt <= 0) return;
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = 0;
@@ -465,6 +507,7 @@ struct Consumer {
 #pragma unroll
             for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
             for (int c = 0; c < KC; ++c) {
+                if (c == gate_chunk && r == 0) mbar_wait(gate_bar, gate_parity, ab, ST_TIMEOUT_FULL);
                 const uint8_t* st = wait_stage();
                 if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
                 if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, xs + c * KCHUNK, lane, acc1);
@@ -487,6 +530,9 @@ struct Consumer {
 template <int D, int CS>
 __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_constant__ Params p) {
     static_assert(D % 8 == 0 && D <= 128, "head_dim must be a multiple of 8, at most 128");
+    // one attention partial: D numerators, running max, denominator, padded so that every
+    // record (and every 4-element group in it) starts on a 16-byte boundary
+    constexpr int PREC = D + 4;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, p.nstage, p.xbuf_floats);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -500,6 +546,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             mbar_init(smem_u32(sm.empty + s), NCWARP);
         }
         mbar_init(smem_u32(sm.xbar), CS > 1 ? CS - 1 : 1);
+        mbar_init(smem_u32(sm.h_go), 1);
+        mbar_init(smem_u32(sm.attn_ready), NHWARP);
         mbar_fence_init();
     }
     __syncthreads();
@@ -586,11 +634,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         int g = g3a;
                         for (int r = 0; r < nr; ++r) {
                             const int n = base + (r < extra ? 1 : 0);
-                            for (int i = 0; i < my3; ++i) {
-                                const int q = me + i * CS;
-                                if (q < KCo) pr.rows_stage(&L->tm_o, q * KCHUNK, g, n);
-                                else pr.rows_stage(&L->tm_down, (q - KCo) * KCHUNK, g, n);
-                            }
+                            // MLP chunks first: the attention chunks are merged by the helper
+                            // warps while these stream
+                            for (int i = nattn; i < my3; ++i)
+                                pr.rows_stage(&L->tm_down, (me + i * CS - KCo) * KCHUNK, g, n);
+                            for (int i = 0; i < nattn; ++i) pr.rows_stage(&L->tm_o, (me + i * CS) * KCHUNK, g, n);
                             g += n;
                         }
                     }
@@ -619,6 +667,142 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             }
         }
         __syncwarp();
+    } else if (warp > NCWARP) {
+        // ========================================================= helper warps
+        // Side work that is pure L2 latency, kept off the consumers' path: in P3, merge the
+        // attention partials of all CTAs into this CTA's attention chunks of xbuf.
+        const int ht = tid - (NCWARP + 1) * 32;
+        const int nmid = my3 - nattn;
+        const int nent = nattn * HPC * pstr;
+        if ((p.phase_mask & PH_P3) && nattn > 0) {
+            // Which partial feeds which of my chunks depends only on (grid, seq): tabulate once.
+            for (int it = ht; it < nent; it += NHTHR) {
+                const int pair = it / pstr, j = it - pair * pstr;
+                const int i = pair / HPC, hh = pair - i * HPC;
+                const int q = me + i * CS;
+                const int h = (q * KCHUNK) / D + hh;
+                int off = -1;
+                if (h < NH && h * D < min((q + 1) * KCHUNK, KVW)) {
+                    if (nch == 0) {
+                        if (j == 0) off = h * PREC;
+                    } else {
+                        const int c = part_of(h * nch, T2, G) + j;
+                        if (c <= part_of((h + 1) * nch - 1, T2, G)) {
+                            const int b0 = part_begin(c, T2, G);
+                            // CTAs between the first and last may own no item at all (T2 < G)
+                            if (part_begin(c + 1, T2, G) != b0) off = (c * MAXL + (h - b0 / nch)) * PREC;
+                        }
+                    }
+                }
+                sm.offs[it] = off;
+            }
+            helper_sync(NHTHR);
+            const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
+            constexpr int ML_ITERS = (WTS_SLOTS + NHTHR - 1) / NHTHR;
+            uint32_t gpar = 0;
+            for (int l = 0; l < p.n_layers; ++l) {
+                mbar_wait(smem_u32(sm.h_go), gpar, ab, ST_TIMEOUT_GRID);
+                gpar ^= 1u;
+                // (max, denominator) of every table entry -> normalised weights in pm[]
+                float mreg[ML_ITERS], lreg[ML_ITERS];
+#pragma unroll
+                for (int k = 0; k < ML_ITERS; ++k) {
+                    const int it = ht + k * NHTHR;
+                    mreg[k] = -INFINITY;
+                    lreg[k] = 0.f;
+                    if (it < nent) {
+                        const int o = sm.offs[it];
+                        if (o >= 0) {
+                            mreg[k] = ld_cg_f32(pbase + o + D);
+                            lreg[k] = ld_cg_f32(pbase + o + D + 1);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < ML_ITERS; ++k) {
+                    const int it = ht + k * NHTHR;
+                    if (it < nent) {
+                        sm.pm[it] = mreg[k];
+                        sm.pl[it] = lreg[k];
+                    }
+                }
+                helper_sync(NHTHR);
+                float wn[ML_ITERS];
+#pragma unroll
+                for (int k = 0; k < ML_ITERS; ++k) {
+                    const int it = ht + k * NHTHR;
+                    wn[k] = 0.f;
+                    if (it < nent && mreg[k] > -INFINITY) {
+                        const int r0 = (it / pstr) * pstr;
+                        float M = -INFINITY, den = 0.f;
+                        for (int j = 0; j < pstr; ++j) M = fmaxf(M, sm.pm[r0 + j]);
+                        for (int j = 0; j < pstr; ++j) {
+                            const float mj = sm.pm[r0 + j];
+                            if (mj > -INFINITY) den = fmaf(exp2f(mj - M), sm.pl[r0 + j], den);
+                        }
+                        wn[k] = exp2f(mreg[k] - M) / den;
+                    }
+                }
+                helper_sync(NHTHR);  // everyone has read pm before it becomes the weight table
+#pragma unroll
+                for (int k = 0; k < ML_ITERS; ++k) {
+                    const int it = ht + k * NHTHR;
+                    if (it < nent) sm.pm[it] = wn[k];
+                }
+                helper_sync(NHTHR);
+                // weighted sums, four consecutive elements per thread, two groups in flight
+                const int nve = nattn * (KCHUNK / 4);
+                for (int v0 = ht; v0 < nve; v0 += 2 * NHTHR) {
+                    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+                    int wrow[2], dd[2], dsti[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int v = v0 + u * NHTHR;
+                        const int i = v / (KCHUNK / 4), k4 = v - i * (KCHUNK / 4);
+                        const int q = me + i * CS;
+                        const int e = q * KCHUNK + k4 * 4;
+                        wrow[u] = -1;
+                        dd[u] = 0;
+                        dsti[u] = (v < nve) ? (nmid + i) * KCHUNK + k4 * 4 : -1;
+                        if (v < nve && e < KVW) {
+                            const int h = e / D;
+                            dd[u] = e - h * D;
+                            wrow[u] = (i * HPC + (h - (q * KCHUNK) / D)) * pstr;
+                        }
+                    }
+                    for (int j0 = 0; j0 < pstr; j0 += 8) {
+                        float4 vv[2][8];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                vv[u][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (wrow[u] >= 0 && j0 + jj < pstr) {
+                                    const int o = sm.offs[wrow[u] + j0 + jj];
+                                    if (o >= 0) vv[u][jj] = ld_cg_f32x4(pbase + o + dd[u]);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                const float w = (wrow[u] >= 0 && j0 + jj < pstr) ? sm.pm[wrow[u] + j0 + jj] : 0.f;
+                                acc[u].x = fmaf(w, vv[u][jj].x, acc[u].x);
+                                acc[u].y = fmaf(w, vv[u][jj].y, acc[u].y);
+                                acc[u].z = fmaf(w, vv[u][jj].z, acc[u].z);
+                                acc[u].w = fmaf(w, vv[u][jj].w, acc[u].w);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        if (dsti[u] >= 0) *reinterpret_cast<float4*>(sm.xbuf + dsti[u]) = acc[u];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(sm.attn_ready));
+            }
+        }
     } else {
         // ======================================================= consumer warps
         Consumer co;
@@ -630,38 +814,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.warp = warp;
         co.lane = lane;
         unsigned epoch = 0;
-        uint32_t xparity = 0;
+        uint32_t xparity = 0, hparity = 0;
         const int pos_off = p.rope_stride * seq;
         const float* cosr = p.cos + pos_off;
         const float* sinr = p.sin + pos_off;
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
         bool need_barrier = false;  // a phase of this launch wrote data the next one reads
-
-        // Which partial feeds which of my attention chunks depends only on (grid, seq):
-        // tabulate it once per launch.
-        if (p.phase_mask & PH_P3) {
-            for (int it = tid; it < nattn * HPC * pstr; it += NCTHR) {
-                const int pair = it / pstr, j = it - pair * pstr;
-                const int i = pair / HPC, hh = pair - i * HPC;
-                const int q = me + i * CS;
-                const int h = (q * KCHUNK) / D + hh;
-                int off = -1;
-                if (h < NH && h * D < min((q + 1) * KCHUNK, KVW)) {
-                    if (nch == 0) {
-                        if (j == 0) off = h * (D + 2);
-                    } else {
-                        const int c = part_of(h * nch, T2, G) + j;
-                        if (c <= part_of((h + 1) * nch - 1, T2, G)) {
-                            const int b0 = part_begin(c, T2, G);
-                            // CTAs between the first and last may own no item at all (T2 < G)
-                            if (part_begin(c + 1, T2, G) != b0) off = (c * MAXL + (h - b0 / nch)) * (D + 2);
-                        }
-                    }
-                }
-                sm.offs[it] = off;
-            }
-            consumer_sync(NCTHR);
-        }
+        // epochs of this launch's exchanges: launch count * (layers + 2) + layer + 1; never 0
+        const unsigned tp_base = (p.tp_size > 1) ? __ldcg(p.tp_launch_count) * static_cast<unsigned>(p.n_layers + 2) : 0u;
 
         const __half* x_first = p.embed ? (p.embed + static_cast<size_t>(__ldcg(p.token_in)) * H) : p.x_in;
 
@@ -734,13 +894,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             L->v_cache[off] = v16;
                             if (p.k_new) p.k_new[h * D + d] = k16;
                             if (p.v_new) p.v_new[h * D + d] = v16;
-                            p.attn_new[h * (D + 2) + d] = __half2float(v16);
+                            p.attn_new[h * PREC + d] = __half2float(v16);
                         }
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                         if (lane == 0) {
-                            p.attn_new[h * (D + 2) + D] = s;
-                            p.attn_new[h * (D + 2) + D + 1] = 1.0f;
+                            p.attn_new[h * PREC + D] = s;
+                            p.attn_new[h * PREC + D + 1] = 1.0f;
                         }
                     }
                 }
@@ -764,7 +924,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         mlbuf[slot * 2 + 1] = l_run;
                     }
                     consumer_sync(NCTHR);
-                    float* dst = p.attn_part + (static_cast<size_t>(cta) * MAXL + (h - h_first)) * (D + 2);
+                    float* dst = p.attn_part + (static_cast<size_t>(cta) * MAXL + (h - h_first)) * PREC;
                     if (tid < D) {
                         float M = -INFINITY;
 #pragma unroll
@@ -909,14 +1069,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             if (p.phase_mask & PH_P3) {
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR2);
-                // ---- this CTA's K slice of [attn ; mid] as fp32 in xbuf, chunk-major.
-                // Everything here is L2 latency, so loads are issued in wide batches.
-                // (1) MLP intermediate: asynchronous 16-byte copies straight into xbuf
+                // ---- this CTA's K slice of [mid ; attn] as fp32 in xbuf, chunk-major, MLP chunks
+                // first.  The helper warps merge the attention partials into the chunks behind
+                // them while the GEMV already runs over the MLP chunks.
+                const int nmid = my3 - nattn;
+                if (tid == 0) mbar_arrive(smem_u32(sm.h_go));
                 if (!(p.p3_flags & F3_MID_F16)) {
-                    const int nvec = (my3 - nattn) * (KCHUNK / 4);
+                    // asynchronous 16-byte copies of the fp32 intermediate straight into xbuf
+                    const int nvec = nmid * (KCHUNK / 4);
                     for (int v = tid; v < nvec; v += NCTHR) {
-                        const int i = nattn + v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
-                        const int e = (me + i * CS - KCo) * KCHUNK + k4 * 4;
+                        const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                        const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;
                         float* dst = sm.xbuf + i * KCHUNK + k4 * 4;
                         if (e + 3 < F) {
                             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
@@ -927,119 +1090,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                     asm volatile("cp.async.commit_group;" ::: "memory");
                 } else {
-                    for (int i0 = nattn; i0 < my3; i0 += 8) {
+                    for (int i0 = 0; i0 < nmid; i0 += 8) {
                         float v[8];
 #pragma unroll
                         for (int ii = 0; ii < 8; ++ii) {
-                            const int e = (me + (i0 + ii) * CS - KCo) * KCHUNK + tid;
-                            v[ii] = (i0 + ii < my3 && e < F) ? __half2float(ld_cg_f16(p.mid_f16_in + e)) : 0.f;
+                            const int e = (me + (nattn + i0 + ii) * CS - KCo) * KCHUNK + tid;
+                            v[ii] = (i0 + ii < nmid && e < F) ? __half2float(ld_cg_f16(p.mid_f16_in + e)) : 0.f;
                         }
 #pragma unroll
                         for (int ii = 0; ii < 8; ++ii)
-                            if (i0 + ii < my3) sm.xbuf[(i0 + ii) * KCHUNK + tid] = v[ii];
+                            if (i0 + ii < nmid) sm.xbuf[(i0 + ii) * KCHUNK + tid] = v[ii];
                     }
-                }
-                // (2) attention merge.  offs[] (which partials feed which of my chunks) was
-                // tabulated at kernel start.  One L2 round trip: every thread fetches the
-                // (max, denominator) pair of one table entry and, without waiting, the
-                // numerators of its elements; then one thread per entry turns the pairs into
-                // normalised weights, and the elements are weighted sums.
-                const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
-                const int nent = nattn * HPC * pstr;
-                constexpr int ML_ITERS = (WTS_SLOTS + NCTHR - 1) / NCTHR;
-                float mreg[ML_ITERS], lreg[ML_ITERS];
-#pragma unroll
-                for (int k = 0; k < ML_ITERS; ++k) {
-                    const int it = tid + k * NCTHR;
-                    mreg[k] = -INFINITY;
-                    lreg[k] = 0.f;
-                    if (it < nent) {
-                        const int o = sm.offs[it];
-                        if (o >= 0) {
-                            mreg[k] = ld_cg_f32(pbase + o + D);
-                            lreg[k] = ld_cg_f32(pbase + o + D + 1);
-                        }
-                    }
-                }
-                bool tables_ready = false;
-                for (int i0 = 0; i0 < nattn || !tables_ready; i0 += 8) {
-                    int wrow[8], dd[8];
-#pragma unroll
-                    for (int ii = 0; ii < 8; ++ii) {
-                        const int q = me + (i0 + ii) * CS;
-                        const int e = q * KCHUNK + tid;
-                        wrow[ii] = -1;
-                        dd[ii] = 0;
-                        if (i0 + ii < nattn && e < KVW) {
-                            const int h = e / D;
-                            dd[ii] = e - h * D;
-                            wrow[ii] = ((i0 + ii) * HPC + (h - (q * KCHUNK) / D)) * pstr;
-                        }
-                    }
-                    float val[8];
-#pragma unroll
-                    for (int ii = 0; ii < 8; ++ii) val[ii] = 0.f;
-                    for (int j0 = 0; j0 < pstr; j0 += 8) {
-                        float v[8][8];
-#pragma unroll
-                        for (int ii = 0; ii < 8; ++ii) {
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) {
-                                v[ii][jj] = 0.f;
-                                if (wrow[ii] >= 0 && j0 + jj < pstr) {
-                                    const int o = sm.offs[wrow[ii] + j0 + jj];
-                                    if (o >= 0) v[ii][jj] = ld_cg_f32(pbase + o + dd[ii]);
-                                }
-                            }
-                        }
-                        if (!tables_ready) {
-#pragma unroll
-                            for (int k = 0; k < ML_ITERS; ++k) {
-                                const int it = tid + k * NCTHR;
-                                if (it < nent) {
-                                    sm.pm[it] = mreg[k];
-                                    sm.pl[it] = lreg[k];
-                                }
-                            }
-                            consumer_sync(NCTHR);
-                            // weight of entry `it` inside its (chunk, head) row, normalised
-                            float wn[ML_ITERS];
-#pragma unroll
-                            for (int k = 0; k < ML_ITERS; ++k) {
-                                const int it = tid + k * NCTHR;
-                                wn[k] = 0.f;
-                                if (it < nent && mreg[k] > -INFINITY) {
-                                    const int r0 = (it / pstr) * pstr;
-                                    float M = -INFINITY, den = 0.f;
-                                    for (int j = 0; j < pstr; ++j) M = fmaxf(M, sm.pm[r0 + j]);
-                                    for (int j = 0; j < pstr; ++j) {
-                                        const float mj = sm.pm[r0 + j];
-                                        if (mj > -INFINITY) den = fmaf(exp2f(mj - M), sm.pl[r0 + j], den);
-                                    }
-                                    wn[k] = exp2f(mreg[k] - M) / den;
-                                }
-                            }
-                            consumer_sync(NCTHR);  // everyone has read pm before it becomes the weight table
-#pragma unroll
-                            for (int k = 0; k < ML_ITERS; ++k) {
-                                const int it = tid + k * NCTHR;
-                                if (it < nent) sm.pm[it] = wn[k];
-                            }
-                            consumer_sync(NCTHR);
-                            tables_ready = true;
-                        }
-#pragma unroll
-                        for (int ii = 0; ii < 8; ++ii) {
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) {
-                                const bool on = wrow[ii] >= 0 && j0 + jj < pstr;
-                                val[ii] = fmaf(on ? sm.pm[wrow[ii] + j0 + jj] : 0.f, v[ii][jj], val[ii]);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int ii = 0; ii < 8; ++ii)
-                        if (i0 + ii < nattn) sm.xbuf[(i0 + ii) * KCHUNK + tid] = val[ii];
                 }
                 // (3) what the epilogue adds to this thread's output row, fetched early
                 float epi_add = 0.f;
@@ -1062,19 +1123,51 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (cnt > 0) {
                     if (my3 > 0) {
                         float* ps = sm.part_s;
-                        co.rows_phase(cnt, my3, sm.xbuf, [&](int g, int r, float v) { ps[g * GRAN + r] = v; });
+                        co.rows_phase(cnt, my3, sm.xbuf, [&](int g, int r, float v) { ps[g * GRAN + r] = v; },
+                                      nattn > 0 ? nmid : -1, smem_u32(sm.attn_ready), hparity);
                     } else {
                         for (int t = tid; t < nrows; t += NCTHR) sm.part_s[t] = 0.f;
                     }
                 }
+                else if (nattn > 0) mbar_wait(smem_u32(sm.attn_ready), hparity, ab, ST_TIMEOUT_FULL);  // keep phases paired
+                hparity ^= 1u;
                 if (tid == 0) trace_mark(p, cta, l, TR_P3_GEMV);
                 const int stride = MAX_P3_ROWS / CS;
                 dsm::reduce_scatter_push<CS>(sm.part_s, sm.recv, stride, nrows, sm.xbar, xparity, tid, NCTHR, ab);
                 xparity ^= 1u;
                 // one output row per thread at most (MAX_P3_ROWS / CS <= consumer threads)
-                if (me + tid * CS < nrows) {
-                    const int row = g3a * GRAN + me + tid * CS;
-                    y[row] = __float2half_rn(dsm::tree_sum<CS>(sm.recv, stride, tid) + epi_add);
+                if (p.tp_size <= 1) {
+                    if (me + tid * CS < nrows) {
+                        const int row = g3a * GRAN + me + tid * CS;
+                        y[row] = __float2half_rn(dsm::tree_sum<CS>(sm.recv, stride, tid) + epi_add);
+                    }
+                } else {
+                    // Tensor parallel: what this CTA holds is one rank's partial of its rows.  The
+                    // same thread of the same CTA owns the same row on every rank, so the all-reduce
+                    // is a thread-to-thread exchange: store my partial row, tagged with this layer's
+                    // epoch, into every peer's buffer (8-byte stores over NVLink), wait (bounded)
+                    // for the N-1 counterparts' words to show the epoch, add the N partials in
+                    // rank order in fp32.  Buffers alternate with the layer's parity, so a slot is
+                    // rewritten only after its reader has sent its next word.
+                    const TpLayout tl{H, p.tp_size};
+                    const unsigned tp_epoch = tp_base + static_cast<unsigned>(l) + 1u;
+                    const int parity = l & 1;
+                    if (me + tid * CS < nrows) {
+                        const int row = g3a * GRAN + me + tid * CS;
+                        const float mine = dsm::tree_sum<CS>(sm.recv, stride, tid);
+                        for (int r = 0; r < p.tp_size; ++r)
+                            if (r != p.tp_rank)
+                                st_ll(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(row) * 8,
+                                      __float_as_uint(mine), tp_epoch);
+                        float sum = 0.f;
+                        for (int r = 0; r < p.tp_size; ++r) {
+                            const float v = (r == p.tp_rank)
+                                ? mine
+                                : __uint_as_float(wait_ll(p.tp_peer[p.tp_rank] + tl.partial_off(parity, r) + static_cast<size_t>(row) * 8, tp_epoch, ab));
+                            sum += v;
+                        }
+                        y[row] = __float2half_rn(sum + epi_add);
+                    }
                 }
                 if (tid == 0) trace_mark(p, cta, l, TR_P3_DONE);
                 need_barrier = true;
@@ -1151,10 +1244,44 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         bi = oi;
                     }
                 }
+                bi += p.vocab_offset;
+                if (p.tp_size > 1) {
+                    // vocabulary shards: every rank sends its (max, index) to all ranks and all
+                    // pick the same winner (largest logit, lowest index on ties)
+                    const TpLayout tl{H, p.tp_size};
+                    const unsigned tp_epoch = tp_base + static_cast<unsigned>(p.n_layers) + 1u;
+                    const int parity = static_cast<int>((tp_base / static_cast<unsigned>(p.n_layers + 2)) & 1u);
+                    if (lane < p.tp_size && lane != p.tp_rank) {
+                        unsigned char* dst = p.tp_peer[lane] + tl.pairs_off(parity, p.tp_rank);
+                        st_ll(dst, __float_as_uint(b), tp_epoch);
+                        st_ll(dst + 8, static_cast<unsigned>(bi), tp_epoch);
+                    }
+                    float rb = -INFINITY;
+                    int rbi = 0x7fffffff;
+                    if (lane == p.tp_rank) {
+                        rb = b;
+                        rbi = bi;
+                    } else if (lane < p.tp_size) {
+                        const unsigned char* src = p.tp_peer[p.tp_rank] + tl.pairs_off(parity, lane);
+                        rb = __uint_as_float(wait_ll(src, tp_epoch, ab));
+                        rbi = static_cast<int>(wait_ll(src + 8, tp_epoch, ab));
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, rb, o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, rbi, o);
+                        if (ov > rb || (ov == rb && oi < rbi)) {
+                            rb = ov;
+                            rbi = oi;
+                        }
+                    }
+                    b = rb;
+                    bi = rbi;
+                }
                 if (lane == 0) {
-                    if (p.token_out) *p.token_out = bi + p.vocab_offset;
-                    p.amax_val[0] = b;  // winner's logit, for vocabulary-sharded callers
-                    p.amax_idx[0] = bi + p.vocab_offset;
+                    if (p.token_out) *p.token_out = bi;
+                    p.amax_val[0] = b;  // winner's logit
+                    p.amax_idx[0] = bi;
                 }
             }
         }
@@ -1169,6 +1296,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     p.sync[0] = 0u;
                     p.sync[1] = 0u;
                     if (p.seq_inc) *p.seq_inc = seq + 1;
+                    if (p.tp_size > 1) *p.tp_launch_count = *p.tp_launch_count + 1u;
                     __threadfence();
                 }
             }

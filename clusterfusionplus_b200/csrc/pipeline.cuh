@@ -145,6 +145,11 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
     return v;
 }
 
+// named barrier over the helper warps only
+__device__ __forceinline__ void helper_sync(int nthreads) {
+    asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+}
+
 // named barrier over the consumer warps only (the producer warp never joins)
 __device__ __forceinline__ void consumer_sync(int nthreads) {
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");

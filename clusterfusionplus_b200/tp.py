@@ -9,10 +9,16 @@ and has no communication backend; this mode is new.  Partition, per layer:
   * LayerNorm parameters, dense bias, down bias and the hidden state are replicated.
 
 Each rank computes LayerNorm redundantly and produces a partial attention + MLP
-output of full width; ONE all-reduce (sum) of that fp16 [hidden] vector per layer
-over NCCL/NVLink combines them, after which every rank adds the residual and the
-two replicated biases exactly once.  The LM head is sharded by vocabulary rows;
-the ranks exchange their (max logit, index) pairs and pick the same winner.
+output of full width; ONE all-reduce (sum) of that [hidden] vector per layer combines
+them, after which every rank adds the residual and the two replicated biases exactly
+once.  The LM head is sharded by vocabulary rows; the ranks exchange their (max logit,
+index) pairs and pick the same winner.
+
+Two data paths: `fused=True` (default) runs the whole token as one launch per rank and
+does the all-reduce inside the kernel -- every CTA stores its fp32 partial rows into the
+peers' exchange buffers over NVLink, publishes a flag and sums the N partials in rank
+order (deterministic, identical on all ranks); `fused=False` is the baseline with one
+NCCL all-reduce of the fp16 partial per layer between two launches.
 """
 from __future__ import annotations
 
@@ -79,7 +85,7 @@ class TPDecoder:
 
     def __init__(self, full_dims: CfDims, local_layers: Sequence[Dict[str, torch.Tensor]],
                  local_head: Dict[str, torch.Tensor], local_caches: Sequence, max_seq: int,
-                 group: Optional[dist.ProcessGroup] = None, use_graph: bool = True):
+                 group: Optional[dist.ProcessGroup] = None, use_graph: bool = True, fused: bool = True):
         self.group = group
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -126,7 +132,18 @@ class TPDecoder:
         self.all_idx = torch.empty(self.size, dtype=torch.int32, device=dev)
         self.use_graph = use_graph
         self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self.launches_per_token = 2 * len(self.layers) + 3  # ours (NCCL's kernels not counted)
+        self.fused = fused
+        if fused:
+            # exchange buffers of all ranks mapped into each other (CUDA IPC over NVLink peer access)
+            mine = (C.c_char * 64)()
+            check(lib.cf_decoder_tp_export(self.handle, C.cast(mine, C.c_void_p)))
+            t = torch.frombuffer(bytearray(mine.raw), dtype=torch.uint8).to(dev)
+            allh = torch.empty(64 * self.size, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh, t, group=self.group)
+            raw = bytes(allh.cpu().numpy().tobytes())
+            check(lib.cf_decoder_tp_connect(self.handle, C.cast(C.create_string_buffer(raw, len(raw)), C.c_void_p)))
+            dist.barrier(group=self.group)
+        self.launches_per_token = 1 if fused else 2 * len(self.layers) + 3  # ours (NCCL's kernels not counted)
 
     def reset(self, seq_len: int, token: int) -> None:
         self.seq_len.fill_(int(seq_len))
@@ -134,6 +151,9 @@ class TPDecoder:
 
     def _enqueue(self) -> None:
         st = torch.cuda.current_stream().cuda_stream
+        if self.fused:
+            check(lib.cf_decoder_step(self.handle, st))
+            return
         for l in range(len(self.layers)):
             check(lib.cf_decoder_layer_partial(self.handle, l, st))
             dist.all_reduce(self.partial, group=self.group)

@@ -106,7 +106,7 @@ int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLa
  * this entry point performs no cudaMalloc / cudaFree and calls no allocating routine:
  * its scratch (fp32 QKV and MLP intermediates, attention partials, barrier words and
  * the layer descriptor with its tensor maps) lives in a static __device__ array of
- * 466,560 bytes that every GPU loading the library holds until exit.
+ * 471,936 bytes that every GPU loading the library holds until exit.
  *   Limits: the built-in models only (at most 32 heads, 4096 QKV columns, ffn 16384)
  *   on at most 160 CTAs; anything larger is rejected with CF_ERR_UNSUPPORTED.
  *   The first call on a device looks up the array's device address and the launch
@@ -225,9 +225,19 @@ int cf_decoder_finalize(int64_t handle);
  * that the caller all-reduces and the (max logit, index) pair of this shard. */
 int cf_decoder_state(int64_t handle, int** token, int** seq_len, float** logits, void** hidden, void** partial,
                      float** shard_max, int** shard_idx);
-/* Enqueue one whole token on `stream` (tp_size == 1). */
+/* Enqueue one whole token on `stream` (tp_size == 1, or a connected tensor-parallel decoder). */
 int cf_decoder_step(int64_t handle, void* stream);
-/* Tensor-parallel pieces, enqueued per layer around the caller's all-reduce of
+/* Tensor-parallel decoders (tp_size 2..8, one process per GPU of one NVLink-connected box):
+ * cf_decoder_step then runs the whole token as ONE launch per rank, with the per-layer
+ * all-reduce done inside the kernel by peer stores into the other ranks' exchange buffers
+ * (no NCCL on the data path).  Set-up, once: every rank calls cf_decoder_tp_export (allocates
+ * its exchange buffer, returns a 64-byte CUDA IPC handle), the host program all-gathers the
+ * handles in rank order (tp_size x 64 bytes) and passes them to cf_decoder_tp_connect.  All
+ * ranks must then enqueue the same sequence of cf_decoder_step calls.  A peer that never shows
+ * up ends the local wait after 1.5 s with device status 7. */
+int cf_decoder_tp_export(int64_t handle, void* ipc_handle_out);
+int cf_decoder_tp_connect(int64_t handle, const void* all_handles);
+/* Tensor-parallel pieces for callers that bring their own all-reduce (NCCL), enqueued per layer around the caller's all-reduce of
  * `partial`: layer_partial -> all-reduce(partial) -> layer_finish; then tail. */
 int cf_decoder_layer_partial(int64_t handle, int layer, void* stream);
 int cf_decoder_layer_finish(int64_t handle, int layer, void* stream);
