@@ -166,6 +166,30 @@ def pythia_2b8_mlp_only(input, attn_output, mlp_intermediate, mlp_down_weight, m
     return out
 
 
+def llama_decoder_layer_sglang(input, residual, weight_qkv, weight_o, k_cache, v_cache, rms_input_weight, eps, cos, sin):
+    """(output[1,4096], residual[1,4096], k_new[1,32,128], v_new[1,32,128]) of the Llama-2-7B attention block.
+    `residual` is updated in place to input + residual (fused add + RMSNorm convention) and returned; the
+    caches hold exactly the sequence (k_cache.size(0) rows) and are not written.
+    Reference: llama_decoder_layer_sglang_sm120, include/pybind.cpp:75-86,281; tests/test_llama.py:149-160."""
+    H, NH, D = 4096, 32, 128
+    kp, rows_k = _cache(k_cache, "k_cache", H)
+    vp, rows_v = _cache(v_cache, "v_cache", H)
+    if rows_k != rows_v:
+        raise RuntimeError("k_cache and v_cache must have the same number of rows")
+    opts = dict(dtype=torch.float16, device=input.device)
+    out = torch.empty((1, H), **opts)
+    res_out = torch.empty((1, H), **opts)
+    k = torch.empty((1, NH, D), **opts)
+    v = torch.empty((1, NH, D), **opts)
+    check(lib.cf_llama_decoder_layer_sglang(
+        _req(input, "input", H), _req(residual, "residual", H), _req(weight_qkv, "weight_qkv", 3 * H * H),
+        _req(weight_o, "weight_o", H * H), kp, vp, rows_k, _req(rms_input_weight, "rms_input_weight", H), float(eps),
+        _req(cos, "cos", D, torch.float32, exact=False), _req(sin, "sin", D, torch.float32, exact=False),
+        out.data_ptr(), res_out.data_ptr(), k.data_ptr(), v.data_ptr(), _stream()))
+    residual.copy_(res_out.view_as(residual))
+    return out, residual, k, v
+
+
 # ---------------------------------------------------------------------------- contexts
 class _DeviceView:
     """Zero-copy torch view of a buffer the C library owns."""

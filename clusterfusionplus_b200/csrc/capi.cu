@@ -751,6 +751,48 @@ int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const Cf
     return launch(nd->ds, d, p, st);
 }
 
+int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const void* weight_qkv,
+                                  const void* weight_o, const void* k_cache, const void* v_cache, int64_t seq_len,
+                                  const void* rms_input_weight, float eps, const float* cos, const float* sin,
+                                  void* output, void* residual_out, void* k_new, void* v_new, void* stream) {
+    const CfDims d = {4096, 32, 128, 128, 0, 0};  // include/5090/llama/config.h:1-4 of the reference
+    if (!input || !weight_qkv || !weight_o || !k_cache || !v_cache || !rms_input_weight || !cos || !sin || !output ||
+        !residual_out)
+        return fail(CF_ERR_INVALID, "null pointer");
+    if (residual && residual == residual_out) return fail(CF_ERR_INVALID, "residual_out must not alias residual");
+    if (seq_len < 1 || seq_len > 0x7fffffff)
+        return fail(CF_ERR_INVALID, "the caches must hold at least one row (got %lld)", (long long)seq_len);
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CfLayerWeights w;
+    memset(&w, 0, sizeof(w));
+    w.qkv_weight = weight_qkv;
+    w.o_weight = weight_o;
+    w.ln_weight = rms_input_weight;
+    LayerDesc* desc;
+    if ((rc = cached_desc(*ds, d, w, const_cast<void*>(k_cache), const_cast<void*>(v_cache), seq_len, st, &desc))) return rc;
+    Params p;
+    base_params(p, d, ds->ws);
+    p.layers = desc;
+    p.n_layers = 1;
+    p.phase_mask = PH_P1 | PH_P2 | PH_P3;
+    p.p3_flags = F3_USE_O;
+    p.arch_flags = AF_RMS_ADD | AF_QKV_PLANAR | AF_NO_APPEND;
+    p.norm_eps = eps;
+    p.x_in = static_cast<const __half*>(input);
+    p.residual_in = static_cast<const __half*>(residual);
+    p.residual_out = static_cast<__half*>(residual_out);
+    p.out = static_cast<__half*>(output);
+    p.k_new = static_cast<__half*>(k_new);
+    p.v_new = static_cast<__half*>(v_new);
+    p.cos = cos;
+    p.sin = sin;
+    p.seq_host = static_cast<int>(seq_len);
+    return launch(*ds, d, p, st);
+}
+
 int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, int phase_mask,
                         void* stream) {
     CfDims d;

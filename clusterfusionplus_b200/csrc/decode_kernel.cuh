@@ -60,6 +60,12 @@ constexpr int MAX_PARTS = 64;               // partials one head may be split in
 constexpr int MAX_TP = 8;                   // ranks of a tensor-parallel group
 
 enum : int { PH_P1 = 1, PH_P2 = 2, PH_P3 = 4, PH_P4 = 8 };
+// variants of the layer for the Llama attention block (reference: include/5090/llama/kernel_sglang.cuh)
+enum : int {
+    AF_RMS_ADD = 1,     // norm = RMSNorm(x + residual) with weight only; the sum is also an output
+    AF_QKV_PLANAR = 2,  // QKV weight rows are [Q of all heads; K of all heads; V of all heads]
+    AF_NO_APPEND = 4,   // the caches hold exactly seq_len rows and are not written
+};
 enum : int {
     F3_USE_O = 1,       // include W_o chunks (attention output) in P3
     F3_USE_DOWN = 2,    // include W_down chunks (MLP) in P3
@@ -129,6 +135,10 @@ struct Params {
     int* token_out;    // next token id (may alias token_in)
     int* seq_inc;      // optional: *seq_inc += 1 at the end of the launch
     int vocab_offset;  // added to the argmax index (vocabulary shards)
+    int arch_flags;    // AF_*
+    float norm_eps;    // RMSNorm epsilon (AF_RMS_ADD)
+    const __half* residual_in;  // [H], AF_RMS_ADD
+    __half* residual_out;       // [H], AF_RMS_ADD: x + residual (must not alias residual_in)
     // optional timeline: [grid][n_layers + 1][TRACE_EVENTS] globaltimer stamps (diagnostics)
     unsigned long long* trace;
     // tensor-parallel exchange over peer memory (tp_size > 1): every rank owns one buffer laid
@@ -425,6 +435,68 @@ __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half
     consumer_sync(NCTHR);
 }
 
+// RMSNorm of (x + residual) into xbuf (fp32): y = s * rsqrt(mean(s^2) + eps) * gamma, s rounded to
+// fp16 first because it is an output of the op (fused add + RMSNorm of the reference:
+// include/5090/llama/kernel_sglang.cuh:96-140).  CTA 0 stores s to sum_out.
+__device__ __forceinline__ void rms_norm_add_to_smem(const __half* x, const __half* residual, const __half* gamma,
+                                                     int H, float eps, float* xbuf, __half* sum_out, float* red,
+                                                     int tid) {
+    constexpr int NV = MAX_H / (NCTHR * 8);
+    float sv[NV][8];
+    uint4 graw[NV];
+    const int nvec = H >> 3;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) graw[j] = __ldg(reinterpret_cast<const uint4*>(gamma + v * 8));
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sv[j][k] = 0.f;
+        if (v < nvec) {
+            const uint4 xr = ld_cg_u32x4(x + v * 8);
+            uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+            if (residual) rr = ld_cg_u32x4(residual + v * 8);
+            const __half2* x2 = reinterpret_cast<const __half2*>(&xr);
+            const __half2* r2 = reinterpret_cast<const __half2*>(&rr);
+            uint4 outraw;
+            __half2* o2 = reinterpret_cast<__half2*>(&outraw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 a = __half22float2(x2[k]), b = __half22float2(r2[k]);
+                o2[k] = __floats2half2_rn(a.x + b.x, a.y + b.y);
+                const float2 f = __half22float2(o2[k]);
+                sv[j][2 * k] = f.x;
+                sv[j][2 * k + 1] = f.y;
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+            }
+            if (sum_out) *reinterpret_cast<uint4*>(sum_out + v * 8) = outraw;
+        }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red, tid) / static_cast<float>(H) + eps);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            const __half2* g2 = reinterpret_cast<const __half2*>(&graw[j]);
+            float o[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 g = __half22float2(g2[k]);
+                o[2 * k] = sv[j][2 * k] * rstd * g.x;
+                o[2 * k + 1] = sv[j][2 * k + 1] * rstd * g.y;
+            }
+            *reinterpret_cast<float4*>(xbuf + v * 8) = make_float4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<float4*>(xbuf + v * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+        }
+    }
+    consumer_sync(NCTHR);
+}
+
 // ---------------------------------------------------------------- producer side
 struct Producer {
     uint32_t ring_addr, full_addr, empty_addr;
@@ -561,7 +633,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         int kv_rows_min = 0x7fffffff;
         if (p.phase_mask & PH_P2)
             for (int l = 0; l < p.n_layers; ++l) kv_rows_min = min(kv_rows_min, p.layers[l].kv_rows);
-        if (seq < 0 || ((p.phase_mask & PH_P2) && seq >= kv_rows_min)) {
+        const int spare = (p.arch_flags & AF_NO_APPEND) ? 0 : 1;  // a free row for the new token
+        if (seq < 0 || ((p.phase_mask & PH_P2) && seq > kv_rows_min - spare)) {
             if (tid == 0) atomicCAS(p.status, 0, ST_BAD_SEQ);
             return;
         }
@@ -843,7 +916,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 }
                 bool have_stats = false;
                 if (qb > qa) {
-                    layer_norm_to_smem(x, L->ln_w, L->ln_b, H, sm.xbuf, sm.red, tid, have_stats);
+                    if (p.arch_flags & AF_RMS_ADD) {
+                        rms_norm_add_to_smem(x, p.residual_in, L->ln_w, H, p.norm_eps, sm.xbuf,
+                                             cta == 0 ? p.residual_out : nullptr, sm.red, tid);
+                    } else {
+                        layer_norm_to_smem(x, L->ln_w, L->ln_b, H, sm.xbuf, sm.red, tid, have_stats);
+                    }
                     have_stats = true;
                     if (tid == 0) trace_mark(p, cta, l, TR_LN_DONE);
                     const __half* bq = L->b_qkv;
@@ -851,7 +929,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     const int row0 = qa * GRAN;
                     co.rows_phase(qb - qa, KC1, sm.xbuf, [&](int g, int r, float v) {
                         const int row = row0 + g * GRAN + r;
-                        dst[row] = v + __half2float(__ldg(bq + row));
+                        const float out = bq ? v + __half2float(__ldg(bq + row)) : v;
+                        if (p.arch_flags & AF_QKV_PLANAR) {
+                            // row of [Q_all; K_all; V_all] -> slot of the per-head [q; k; v] scratch
+                            const int part = row / KVW, rem = row - part * KVW;
+                            const int h = rem / D;
+                            dst[h * 3 * D + part * D + (rem - h * D)] = out;
+                        } else {
+                            dst[row] = out;
+                        }
                     });
                     consumer_sync(NCTHR);  // xbuf is rewritten next
                 }
@@ -890,8 +976,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             const __half v16 = __float2half_rn(ld_cg_f32(qv + 2 * D + d));
                             s = fmaf(qd, __half2float(k16), s);
                             const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
-                            L->k_cache[off] = k16;
-                            L->v_cache[off] = v16;
+                            if (!(p.arch_flags & AF_NO_APPEND)) {
+                                L->k_cache[off] = k16;
+                                L->v_cache[off] = v16;
+                            }
                             if (p.k_new) p.k_new[h * D + d] = k16;
                             if (p.v_new) p.v_new[h * D + d] = v16;
                             p.attn_new[h * PREC + d] = __half2float(v16);
@@ -967,10 +1055,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                                 sm.kv_s[(part - 1) * D + d] = __half2float(h16);
                                 const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
                                 if (part == 1) {
-                                    L->k_cache[off] = h16;
+                                    if (!(p.arch_flags & AF_NO_APPEND)) L->k_cache[off] = h16;
                                     if (p.k_new) p.k_new[h * D + d] = h16;
                                 } else {
-                                    L->v_cache[off] = h16;
+                                    if (!(p.arch_flags & AF_NO_APPEND)) L->v_cache[off] = h16;
                                     if (p.v_new) p.v_new[h * D + d] = h16;
                                 }
                             }

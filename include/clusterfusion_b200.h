@@ -120,6 +120,22 @@ int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLa
 int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
                                     void* stream);
 
+/* Llama-2-7B attention block, one token at batch 1 (hidden 4096, 32 heads x 128, full NeoX
+ * RoPE, no biases): residual_out = input + residual (fp16; residual may be NULL = zeros);
+ * h = RMSNorm(residual_out, rms_input_weight, eps); q,k,v = weight_qkv h with rows laid out
+ * [Q of all heads; K of all heads; V of all heads]; rotate-half RoPE with cos/sin[128];
+ * attention over the seq_len rows of k_cache / v_cache ([seq_len, 4096], NOT written) plus the
+ * new token; output = weight_o attn (weight_o [4096, 4096] in nn.Linear layout).  k_new is
+ * post-RoPE, [32,128].  residual_out must not alias residual.
+ * Replaces llama_decoder_layer_sglang_sm120 (include/pybind.cpp:75-86;
+ * include/5090/llama/llama_kernel_sglang_dispatch.cu:4-151; kernel_sglang.cuh:20-634).
+ * The reference's other Llama entry points (transposed-weight llama_decoder_layer, paged
+ * batch llama_decoder_layer_batch_decode_sglang) are not provided. */
+int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const void* weight_qkv,
+                                  const void* weight_o, const void* k_cache, const void* v_cache, int64_t seq_len,
+                                  const void* rms_input_weight, float eps, const float* cos, const float* sin,
+                                  void* output, void* residual_out, void* k_new, void* v_new, void* stream);
+
 /* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
  * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one
  * launch, reading what earlier phases left in the library's scratch.  Used by the

@@ -89,3 +89,20 @@ def test_oracle_model_step_equals_layer_composition():
                                       cos[0], sin[0], 0)
     assert torch.allclose(hid, x, atol=1e-6)
     assert torch.allclose(logits, O.final_logits_fp32(x, head).reshape(-1), atol=1e-6)
+
+
+def test_llama_oracle_matches_hf_attention():
+    """The Llama attention-block restatement against transformers' LlamaRMSNorm + LlamaAttention."""
+    from oracle import llama_oracle as L
+    NH, D, seq = 4, 32, 9
+    H = NH * D
+    x, r = O.seeded_normal((1, H), 1), O.seeded_normal((1, H), 2)
+    wq, wo = O.seeded_normal((3 * H, H), 3, std=0.1), O.seeded_normal((H, H), 4, std=0.1)
+    g = O.seeded_normal((H,), 5, mean=1.0, std=0.1)
+    k, v = O.seeded_normal((seq, H), 6), O.seeded_normal((seq, H), 7)
+    ang = torch.rand(D // 2, generator=torch.Generator().manual_seed(8)) * 6.28
+    cos, sin = torch.cat([ang.cos(), ang.cos()]), torch.cat([ang.sin(), ang.sin()])
+    a = L.llama_attn_block_fp32(x, r, wq, wo, k, v, g, 1e-6, cos, sin, NH, D)
+    b = L.hf_llama_attn_block(x, r, wq, wo, k, v, g, 1e-6, cos, sin, NH, D)
+    for p, q in zip(a, b):
+        assert O.compare(p, q)[0] < 1e-5
