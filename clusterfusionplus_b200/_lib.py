@@ -77,6 +77,8 @@ SIGNATURES = {
     "cf_decoder_state": (C.c_int, [C.c_int64] + [_P(C.c_void_p)] * 7),
     "cf_decoder_tp_export": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_tp_connect": (C.c_int, [C.c_int64, C.c_void_p]),
+    "cf_decoder_tp_buffer": (C.c_int, [C.c_int64, _P(C.c_void_p), _P(C.c_int64)]),
+    "cf_decoder_tp_connect_pointers": (C.c_int, [C.c_int64, _P(C.c_void_p)]),
     "cf_decoder_step": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_layer_partial": (C.c_int, [C.c_int64, C.c_int, C.c_void_p]),
     "cf_decoder_layer_finish": (C.c_int, [C.c_int64, C.c_int, C.c_void_p]),

@@ -534,6 +534,7 @@ struct Decoder {
     unsigned char* tp_peer[MAX_TP] = {nullptr};  // every rank's buffer as mapped here ([tp_rank] == tp_local)
     unsigned* tp_count = nullptr;
     bool tp_connected = false;
+    bool tp_ipc = false;  // peers were opened through CUDA IPC (and must be closed)
 };
 
 std::unordered_map<int64_t, Decoder*> g_decoders;
@@ -1200,8 +1201,38 @@ int cf_decoder_tp_connect(int64_t handle, const void* all_handles) {
             return fail(CF_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d failed: %s (peer access over NVLink is required)", r,
                         cudaGetErrorString(e));
         dc->tp_peer[r] = static_cast<unsigned char*>(ptr);
+        dc->tp_ipc = true;
     }
     dc->tp_connected = true;
+    return CF_OK;
+}
+
+int cf_decoder_tp_connect_pointers(int64_t handle, void* const* peer_buffers) {
+    Decoder* dc;
+    int rc = find_decoder(handle, &dc);
+    if (rc) return rc;
+    if (!peer_buffers) return fail(CF_ERR_INVALID, "null pointer table");
+    if (!dc->tp_local) return fail(CF_ERR_INVALID, "call cf_decoder_tp_export first");
+    for (int r = 0; r < dc->cfg.tp_size; ++r) {
+        if (r == dc->cfg.tp_rank) {
+            dc->tp_peer[r] = dc->tp_local;
+        } else {
+            if (!peer_buffers[r]) return fail(CF_ERR_INVALID, "null buffer for rank %d", r);
+            if (reinterpret_cast<uintptr_t>(peer_buffers[r]) & 15) return fail(CF_ERR_INVALID, "buffer of rank %d not 16-byte aligned", r);
+            dc->tp_peer[r] = static_cast<unsigned char*>(peer_buffers[r]);
+        }
+    }
+    dc->tp_connected = true;
+    return CF_OK;
+}
+
+int cf_decoder_tp_buffer(int64_t handle, void** buffer, int64_t* bytes) {
+    Decoder* dc;
+    int rc = find_decoder(handle, &dc);
+    if (rc) return rc;
+    if (!dc->tp_local) return fail(CF_ERR_INVALID, "call cf_decoder_tp_export first");
+    if (buffer) *buffer = dc->tp_local;
+    if (bytes) *bytes = static_cast<int64_t>(TpLayout{dc->cfg.dims.hidden, dc->cfg.tp_size}.bytes());
     return CF_OK;
 }
 
@@ -1316,8 +1347,9 @@ int cf_decoder_destroy(int64_t handle) {
         g_decoders.erase(it);
     }
     cudaDeviceSynchronize();
-    for (int r = 0; r < MAX_TP; ++r)
-        if (dc->tp_peer[r] && dc->tp_peer[r] != dc->tp_local) cudaIpcCloseMemHandle(dc->tp_peer[r]);
+    if (dc->tp_ipc)
+        for (int r = 0; r < MAX_TP; ++r)
+            if (dc->tp_peer[r] && dc->tp_peer[r] != dc->tp_local) cudaIpcCloseMemHandle(dc->tp_peer[r]);
     if (dc->tp_local) cudaFree(dc->tp_local);
     cudaFree(dc->token_d);
     cudaFree(dc->ws.base);

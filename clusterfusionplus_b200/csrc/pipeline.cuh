@@ -22,7 +22,13 @@ enum : int {
     ST_TIMEOUT_PEER = 7,    // tensor-parallel peer flag never arrived
 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;  // 1.5 s
+// Wait limits are staggered so that the wait that names the root cause gives up first: a peer
+// GPU that never answers (1.0 s) before the barriers that then cannot complete (1.5 s) before
+// the TMA ring, which stalls behind everything else (2.0 s).
+constexpr unsigned long long WAIT_LIMIT_NS = 2000ull * 1000ull * 1000ull;
+__device__ __forceinline__ unsigned long long wait_limit_ns(int code) {
+    return code == 7 ? 1000ull * 1000ull * 1000ull : (code == 3 || code == 4) ? 1500ull * 1000ull * 1000ull : WAIT_LIMIT_NS;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -93,7 +99,7 @@ __device__ __forceinline__ bool wait_bounded(Probe probe, const AbortCtl& a, int
     while (!probe()) {
         if ((++it & 0xffu) == 0) {
             if (*a.flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > wait_limit_ns(code)) {
                 raise_abort(a, code);
                 return false;
             }

@@ -250,9 +250,15 @@ int cf_decoder_step(int64_t handle, void* stream);
  * its exchange buffer, returns a 64-byte CUDA IPC handle), the host program all-gathers the
  * handles in rank order (tp_size x 64 bytes) and passes them to cf_decoder_tp_connect.  All
  * ranks must then enqueue the same sequence of cf_decoder_step calls.  A peer that never shows
- * up ends the local wait after 1.5 s with device status 7. */
+ * up ends the local wait after 1.0 s with device status 7. */
 int cf_decoder_tp_export(int64_t handle, void* ipc_handle_out);
 int cf_decoder_tp_connect(int64_t handle, const void* all_handles);
+/* Same, for a host program that drives all GPUs from ONE process with peer access enabled
+ * (cudaDeviceEnablePeerAccess): after cf_decoder_tp_export on every decoder, read each one's
+ * exchange buffer with cf_decoder_tp_buffer and hand every decoder the table of tp_size device
+ * pointers in rank order (the entry of its own rank is ignored). */
+int cf_decoder_tp_buffer(int64_t handle, void** buffer, int64_t* bytes);
+int cf_decoder_tp_connect_pointers(int64_t handle, void* const* peer_buffers);
 /* Tensor-parallel pieces for callers that bring their own all-reduce (NCCL), enqueued per layer around the caller's all-reduce of
  * `partial`: layer_partial -> all-reduce(partial) -> layer_finish; then tail. */
 int cf_decoder_layer_partial(int64_t handle, int layer, void* stream);
