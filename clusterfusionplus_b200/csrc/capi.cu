@@ -70,7 +70,8 @@ EncodeTiledFn get_encode() {
 
 // fp16 row-major [outer, inner] with `row_stride` elements between rows
 int encode_2d(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride,
-              uint32_t box_inner, uint32_t box_outer) {
+              uint32_t box_inner, uint32_t box_outer,
+              CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return fail(CF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return fail(CF_ERR_INVALID, "tensor base not 16-byte aligned");
@@ -80,8 +81,7 @@ int encode_2d(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer, 
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t es[2] = {1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(CF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return CF_OK;
 }
@@ -381,8 +381,12 @@ int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, voi
     if (w.mlp_up_weight && (rc = encode_2d(&L.tm_up, w.mlp_up_weight, d.hidden, d.ffn, d.hidden, KCHUNK, GRAN))) return rc;
     if (w.o_weight && (rc = encode_2d(&L.tm_o, w.o_weight, KVW, d.hidden, KVW, KCHUNK, GRAN))) return rc;
     if (w.mlp_down_weight && (rc = encode_2d(&L.tm_down, w.mlp_down_weight, d.ffn, d.hidden, d.ffn, KCHUNK, GRAN))) return rc;
-    if (k_cache && (rc = encode_2d(&L.tm_k, k_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE))) return rc;
-    if (v_cache && (rc = encode_2d(&L.tm_v, v_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE))) return rc;
+    // a head's slice of a cache row is head_dim * 2 bytes: promote L2 fetches to 256 B only when
+    // that is a whole number of 256-byte lines (head_dim 128), otherwise fetch exact sectors
+    const CUtensorMapL2promotion kvp =
+        (d.head_dim * 2) % 256 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    if (k_cache && (rc = encode_2d(&L.tm_k, k_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE, kvp))) return rc;
+    if (v_cache && (rc = encode_2d(&L.tm_v, v_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE, kvp))) return rc;
     L.ln_w = static_cast<const __half*>(w.ln_weight);
     L.ln_b = static_cast<const __half*>(w.ln_bias);
     L.pln_w = static_cast<const __half*>(w.post_ln_weight);

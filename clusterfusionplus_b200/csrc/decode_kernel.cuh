@@ -12,7 +12,7 @@
 //   P1  LayerNorm (both norms share mean/rstd) -> {QKV, MLP-up} GEMV, output rows
 //       partitioned over ALL CTAs (no split-K), + bias (+ tanh-GELU for MLP-up)
 //   --- grid barrier ---
-//   P2  partial NeoX RoPE, KV append, flash-decode over (head, 64-row chunk)
+//   P2  partial NeoX RoPE, KV append, flash-decode over (head, 128-row chunk)
 //       items spread evenly over all CTAs, per-CTA partial (m, l, acc) in fp32
 //   --- grid barrier ---
 //   P3  merge attention partials, {O-proj, MLP-down} as ONE GEMV over
@@ -51,7 +51,8 @@ constexpr int NCTHR = NCWARP * 32;          // consumer threads
 constexpr int NHWARP = 3;                   // helper warps: latency-bound side work off the consumers' path
 constexpr int NHTHR = NHWARP * 32;
 constexpr int NTHREADS = NCTHR + 32 + NHTHR;  // consumers + producer warp + helpers = 12 warps (register-file granule)
-constexpr int KV_TILE = 64;                 // cache rows per attention item
+constexpr int KV_TILE = 128;                // cache rows per attention item (K tile and V tile are separate stages)
+constexpr int KV_RPH = KV_TILE / (2 * NCWARP);  // rows per half-warp per item
 constexpr int MAXL = 4;                     // attention partial slots per CTA
 constexpr int MAX_P3_ROWS = 256;            // output rows one cluster may own in P3
 constexpr int MAX_H = 4096;                 // LayerNorm register staging limit
@@ -530,18 +531,21 @@ struct Producer {
             g += n;
         }
     }
+    // one attention item = two stages: the K tile, then the V tile of the same 128 rows
     template <int D>
     __device__ __forceinline__ void kv_stage(const CUtensorMap* tmk, const CUtensorMap* tmv, int h, int ch) {
-        acquire();
-        if (*ab.flag) return;
-        const uint32_t bar = full_addr + cur.stage * 8;
         constexpr uint32_t TILE = KV_TILE * D * 2;
-        mbar_arrive_expect_tx(bar, 2 * TILE);
-        const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
-        tma_load_2d(dst, tmk, h * D, ch * KV_TILE, bar, policy);
-        tma_load_2d(dst + TILE, tmv, h * D, ch * KV_TILE, bar, policy);
-        cur.advance();
-        ++issued;
+        static_assert(TILE <= STAGE_BYTES, "a K or V tile must fit one ring stage");
+#pragma unroll
+        for (int kv = 0; kv < 2; ++kv) {
+            acquire();
+            if (*ab.flag) return;
+            const uint32_t bar = full_addr + cur.stage * 8;
+            mbar_arrive_expect_tx(bar, TILE);
+            tma_load_2d(ring_addr + cur.stage * STAGE_BYTES, kv ? tmv : tmk, h * D, ch * KV_TILE, bar, policy);
+            cur.advance();
+            ++issued;
+        }
     }
 };
 
@@ -1072,13 +1076,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         m_run = -INFINITY;
                         l_run = 0.f;
                     }
-                    const uint8_t* st = co.wait_stage();
-                    const __half* kt = reinterpret_cast<const __half*>(st);
-                    const __half* vt = kt + KV_TILE * D;
-                    const int r0 = warp * 8 + hw * 4;
-                    float s[4];
+                    const __half* kt = reinterpret_cast<const __half*>(co.wait_stage());
+                    const int r0 = warp * (2 * KV_RPH) + hw * KV_RPH;
+                    float s[KV_RPH];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < KV_RPH; ++j) {
                         float d = 0.f;
                         if (dim_ok) {
                             const uint4 raw = *reinterpret_cast<const uint4*>(kt + (r0 + j) * D + l16 * 8);
@@ -1092,28 +1094,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                         s[j] = d;
                     }
+                    co.release_stage();  // K tile consumed: scores are in registers
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int o = 8; o > 0; o >>= 1) {
 #pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
+                        for (int j = 0; j < KV_RPH; ++j) s[j] += __shfl_xor_sync(0xffffffffu, s[j], o);
                     }
                     const int grow = ch * KV_TILE + r0;
                     float mx = m_run;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int j = 0; j < KV_RPH; ++j) {
                         if (grow + j >= seq) s[j] = -INFINITY;
                         mx = fmaxf(mx, s[j]);
                     }
+                    float sc = 1.f;
                     if (mx > -INFINITY) {
-                        const float sc = exp2f(m_run - mx);
+                        sc = exp2f(m_run - mx);
+                        m_run = mx;
+#pragma unroll
+                        for (int j = 0; j < KV_RPH; ++j) s[j] = (grow + j < seq) ? exp2f(s[j] - mx) : 0.f;
+                    }
+                    const __half* vt = reinterpret_cast<const __half*>(co.wait_stage());
+                    if (mx > -INFINITY) {
                         l_run *= sc;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) acc[k] *= sc;
-                        m_run = mx;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (grow + j < seq) {
-                                const float pj = exp2f(s[j] - mx);
+                        for (int j = 0; j < KV_RPH; ++j) {
+                            if (grow + j < seq) {  // rows past the sequence may hold anything: never touch them
+                                const float pj = s[j];
                                 l_run += pj;
                                 if (dim_ok) {
                                     const uint4 raw = *reinterpret_cast<const uint4*>(vt + (r0 + j) * D + l16 * 8);

@@ -99,7 +99,7 @@ def test_partition_is_exact_and_invertible(total, parts):
 def test_attention_item_split_bounds(NH, G, seq):
     """A CTA's items touch at most MAXL = 4 heads, a head is split into at most
     ceil(G / NH) + 2 partials: the sizes the kernel's scratch is laid out for."""
-    nch = -(-seq // 64)
+    nch = -(-seq // 128)   # KV_TILE
     T = NH * nch
     pstr = -(-G // NH) + 2
     for c in range(G):
