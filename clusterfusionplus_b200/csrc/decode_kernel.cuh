@@ -54,9 +54,9 @@ constexpr int NTHREADS = NCTHR + 32 + NHTHR;  // consumers + producer warp + hel
 constexpr int KV_TILE = 128;                // cache rows per attention item (K tile and V tile are separate stages)
 constexpr int KV_RPH = KV_TILE / (2 * NCWARP);  // rows per half-warp per item
 constexpr int MAXL = 4;                     // attention partial slots per CTA
-constexpr int MAX_P3_ROWS = 256;            // output rows one cluster may own in P3
+constexpr int MAX_P3_ROWS = 128;            // output rows one cluster may own in P3
 constexpr int MAX_H = 4096;                 // LayerNorm register staging limit
-constexpr int WTS_SLOTS = 640;              // (attention chunk, head, partial) merge weights one CTA may need
+constexpr int WTS_SLOTS = 256;              // (attention chunk, head, partial) merge weights one CTA may need
 constexpr int MAX_PARTS = 64;               // partials one head may be split into
 constexpr int MAX_TP = 8;                   // ranks of a tensor-parallel group
 

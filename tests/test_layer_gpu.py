@@ -46,8 +46,8 @@ def run_and_check(model, seq, rows=None, split=False, **kw):
     return out, kn, vn
 
 
-# empty cache, tile edges of the 64-row attention chunks, the reference test's 129, a full config-1 cache
-@pytest.mark.parametrize("seq", [0, 1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 200, 1024, 4095])
+# empty cache, tile edges of the 128-row attention chunks (and of the earlier 64-row ones), the reference test's 129, a full config-1 cache
+@pytest.mark.parametrize("seq", [0, 1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 200, 255, 256, 257, 1024, 4095])
 def test_layer_2b8_vs_oracle(cuda_device, seq):
     run_and_check("2b8", seq)
 
