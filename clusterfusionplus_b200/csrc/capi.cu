@@ -86,6 +86,14 @@ int encode_2d(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer, 
     return CF_OK;
 }
 
+// contiguous row-major weight [rows, cols]: boxes of 8, 32 and 64 rows x 256 columns
+int encode_weight(WeightMaps* m, const void* ptr, uint64_t cols, uint64_t rows) {
+    int rc;
+    if ((rc = encode_2d(&m->r8, ptr, cols, rows, cols, KCHUNK, GRAN))) return rc;
+    if ((rc = encode_2d(&m->r32, ptr, cols, rows, cols, KCHUNK, 4 * GRAN))) return rc;
+    return encode_2d(&m->r64, ptr, cols, rows, cols, KCHUNK, 8 * GRAN);
+}
+
 struct Workspace {
     void* base = nullptr;
     float *qkv_f32 = nullptr, *mid_f32 = nullptr, *attn_part = nullptr, *attn_new = nullptr, *amax_val = nullptr;
@@ -282,7 +290,7 @@ int check_dims(const CfDims& d) {
 int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* nstage, int* xbuf_floats) {
     const int KVW = d.heads * d.head_dim;
     const int kc3 = ((p3_flags & F3_USE_O) ? ceil_div(KVW, KCHUNK) : 0) + ((p3_flags & F3_USE_DOWN) ? ceil_div(d.ffn, KCHUNK) : 0);
-    int xb = d.hidden;
+    int xb = 2 * d.hidden;  // both LayerNorm outputs of a layer side by side
     if (ceil_div(kc3, cs) * KCHUNK > xb) xb = ceil_div(kc3, cs) * KCHUNK;
     if (16 * d.head_dim + 32 > xb) xb = 16 * d.head_dim + 32;
     xb = (xb + 3) / 4 * 4;
@@ -310,6 +318,23 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         const int pstr = ceil_div(c.grid, d.heads) + 2;
         if (pstr > MAX_PARTS || ceil_div(kco, c.cs) * hpc * pstr > WTS_SLOTS)
             return fail(CF_ERR_UNSUPPORTED, "attention merge table too small for %d heads on %d CTAs", d.heads, c.grid);
+    }
+    {
+        // joint QKV + MLP-up row split: usable when the derived up ranges are monotone
+        const int ngq = 3 * d.heads * d.head_dim / GRAN, ng1 = ngq + d.ffn / GRAN;
+        bool ok = true;
+        int prev = 0;
+        for (int i = 1; i <= c.grid && ok; ++i) {
+            const int u = part_begin(i, ng1, c.grid) - part_begin(i, ngq, c.grid);
+            ok = u >= prev;
+            prev = u;
+        }
+        // Measured on B200: with long P1 streams (>= 20 granules per CTA: Pythia-6.9B on one GPU) grouping
+        // the CTAs by matrix is ~0.4 % faster; with short ones (Pythia-2.8B, tensor-parallel shards) hiding
+        // the barrier behind the MLP-up rows wins ~2 %.
+        p.p1_joint = (ng1 / c.grid >= 20) ? 2 : (ok ? 1 : 0);
+        const int mode = env_int("CFB200_P1_MODE", -1);
+        if (mode == 0 || mode == 2 || (mode == 1 && ok)) p.p1_joint = mode;
     }
     rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats);
     if (rc != CF_OK) return rc;
@@ -377,10 +402,10 @@ int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, voi
     memset(&L, 0, sizeof(L));
     const int KVW = d.heads * d.head_dim;
     int rc;
-    if (w.qkv_weight && (rc = encode_2d(&L.tm_qkv, w.qkv_weight, d.hidden, 3 * KVW, d.hidden, KCHUNK, GRAN))) return rc;
-    if (w.mlp_up_weight && (rc = encode_2d(&L.tm_up, w.mlp_up_weight, d.hidden, d.ffn, d.hidden, KCHUNK, GRAN))) return rc;
-    if (w.o_weight && (rc = encode_2d(&L.tm_o, w.o_weight, KVW, d.hidden, KVW, KCHUNK, GRAN))) return rc;
-    if (w.mlp_down_weight && (rc = encode_2d(&L.tm_down, w.mlp_down_weight, d.ffn, d.hidden, d.ffn, KCHUNK, GRAN))) return rc;
+    if (w.qkv_weight && (rc = encode_weight(&L.tm_qkv, w.qkv_weight, d.hidden, 3 * KVW))) return rc;
+    if (w.mlp_up_weight && (rc = encode_weight(&L.tm_up, w.mlp_up_weight, d.hidden, d.ffn))) return rc;
+    if (w.o_weight && (rc = encode_weight(&L.tm_o, w.o_weight, KVW, d.hidden))) return rc;
+    if (w.mlp_down_weight && (rc = encode_weight(&L.tm_down, w.mlp_down_weight, d.ffn, d.hidden))) return rc;
     // a head's slice of a cache row is head_dim * 2 bytes: promote L2 fetches to 256 B only when
     // that is a whole number of 256-byte lines (head_dim 128), otherwise fetch exact sectors
     const CUtensorMapL2promotion kvp =
@@ -1122,9 +1147,7 @@ int cf_decoder_set_head(int64_t handle, const CfHeadWeights* head) {
         return fail(CF_ERR_INVALID, "null head pointer");
     if (dc->cfg.dims.vocab <= 0) return fail(CF_ERR_INVALID, "decoder was created with vocab 0");
     memset(&dc->tail_h, 0, sizeof(TailDesc));
-    if ((rc = encode_2d(&dc->tail_h.tm_head, head->embed_out, dc->cfg.dims.hidden, dc->cfg.dims.vocab,
-                        dc->cfg.dims.hidden, KCHUNK, GRAN)))
-        return rc;
+    if ((rc = encode_weight(&dc->tail_h.tm_head, head->embed_out, dc->cfg.dims.hidden, dc->cfg.dims.vocab))) return rc;
     dc->tail_h.fln_w = static_cast<const __half*>(head->final_ln_weight);
     dc->tail_h.fln_b = static_cast<const __half*>(head->final_ln_bias);
     dc->tail_h.vocab = dc->cfg.dims.vocab;

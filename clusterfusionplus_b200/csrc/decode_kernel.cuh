@@ -77,8 +77,15 @@ enum : int {
 };
 
 // Per-layer descriptor, resident in device memory.
+// A weight matrix is described three times, with boxes of 8, 32 and 64 rows (x 256 K elements):
+// a stage's run of consecutive granules is fetched with the fewest TMA operations.
+struct WeightMaps {
+    CUtensorMap r8, r32, r64;
+};
+
 struct alignas(128) LayerDesc {
-    CUtensorMap tm_qkv, tm_up, tm_o, tm_down, tm_k, tm_v;
+    WeightMaps tm_qkv, tm_up, tm_o, tm_down;
+    CUtensorMap tm_k, tm_v;
     const __half *ln_w, *ln_b, *pln_w, *pln_b;
     const __half *b_qkv, *b_up, *b_o, *b_down;
     __half *k_cache, *v_cache;
@@ -87,7 +94,7 @@ struct alignas(128) LayerDesc {
 };
 
 struct alignas(128) TailDesc {
-    CUtensorMap tm_head;
+    WeightMaps tm_head;
     const __half *fln_w, *fln_b;
     int vocab;
     int pad_[11];
@@ -136,6 +143,8 @@ struct Params {
     int* token_out;    // next token id (may alias token_in)
     int* seq_inc;      // optional: *seq_inc += 1 at the end of the launch
     int vocab_offset;  // added to the argmax index (vocabulary shards)
+    int p1_joint;      // P1 row split: 1 = every CTA QKV share then up share, jointly balanced (host verified it
+                       // is monotone), 0 = the same with independent even splits, 2 = grouped (QKV CTAs, up CTAs)
     int arch_flags;    // AF_*
     float norm_eps;    // RMSNorm epsilon (AF_RMS_ADD)
     const __half* residual_in;  // [H], AF_RMS_ADD
@@ -352,6 +361,25 @@ __device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned& epoch,
     consumer_sync(NCTHR);
 }
 
+// Split form of the same barrier: count in now, wait later.  Work that does not depend on the
+// other CTAs goes between the two calls.  All consumer threads call both.
+__device__ __forceinline__ void grid_arrive(unsigned* counter, unsigned& epoch, int tid) {
+    consumer_sync(NCTHR);
+    epoch += 1;
+    if (tid == 0) {
+        __threadfence();
+        atomicAdd(counter, 1u);
+    }
+}
+__device__ __forceinline__ void grid_wait(unsigned* counter, unsigned epoch, unsigned G, int tid, const AbortCtl& ab) {
+    if (tid == 0) {
+        const unsigned target = epoch * G;
+        wait_bounded([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
+        __threadfence();
+    }
+    consumer_sync(NCTHR);
+}
+
 // LayerNorm of x[H] into xbuf (fp32).  which = 0: input norm, 1: post-attention
 // norm.  mean/rstd are computed once per layer (two-pass, fp32) and kept in red[32..33].
 __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half* gamma, const __half* beta, int H,
@@ -436,6 +464,90 @@ __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half
     consumer_sync(NCTHR);
 }
 
+// LayerNorm of x[H] into out1 with (gamma1, beta1) and, when out2 != nullptr, into out2 with
+// (gamma2, beta2) from the same mean / rstd: the input norm and the post-attention norm of a
+// parallel-residual layer see the same input.  Two-pass statistics in fp32.
+__device__ __forceinline__ void layer_norm2_to_smem(const __half* x, const __half* gamma1, const __half* beta1,
+                                                    const __half* gamma2, const __half* beta2, int H, float* out1,
+                                                    float* out2, float* red, int tid) {
+    constexpr int NV = MAX_H / (NCTHR * 8);
+    float xv[NV][8];
+    uint4 g1[NV], b1[NV], g2[NV], b2[NV];
+    const int nvec = H >> 3;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            g1[j] = __ldg(reinterpret_cast<const uint4*>(gamma1 + v * 8));
+            b1[j] = __ldg(reinterpret_cast<const uint4*>(beta1 + v * 8));
+            if (out2) {
+                g2[j] = __ldg(reinterpret_cast<const uint4*>(gamma2 + v * 8));
+                b2[j] = __ldg(reinterpret_cast<const uint4*>(beta2 + v * 8));
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+            const uint4 raw = ld_cg_u32x4(x + v * 8);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(h2[k]);
+                xv[j][2 * k] = f.x;
+                xv[j][2 * k + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) xv[j][k] = 0.f;
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += xv[j][k];
+    const float mean = block_sum(s, red, tid) / static_cast<float>(H);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float d = xv[j][k] - mean;
+                ss = fmaf(d, d, ss);
+            }
+        }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red, tid) / static_cast<float>(H) + 1e-5f);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int v = j * NCTHR + tid;
+        if (v < nvec) {
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                if (which == 1 && !out2) break;
+                const __half2* gg = reinterpret_cast<const __half2*>(which ? &g2[j] : &g1[j]);
+                const __half2* bb = reinterpret_cast<const __half2*>(which ? &b2[j] : &b1[j]);
+                float o[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 g = __half22float2(gg[k]);
+                    const float2 b = __half22float2(bb[k]);
+                    o[2 * k] = (xv[j][2 * k] - mean) * rstd * g.x + b.x;
+                    o[2 * k + 1] = (xv[j][2 * k + 1] - mean) * rstd * g.y + b.y;
+                }
+                float* dst = (which ? out2 : out1) + v * 8;
+                *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+            }
+        }
+    }
+    consumer_sync(NCTHR);
+}
+
 // RMSNorm of (x + residual) into xbuf (fp32): y = s * rsqrt(mean(s^2) + eps) * gamma, s rounded to
 // fp16 first because it is an output of the op (fused add + RMSNorm of the reference:
 // include/5090/llama/kernel_sglang.cuh:96-140).  CTA 0 stores s to sum_out.
@@ -509,25 +621,57 @@ struct Producer {
     __device__ __forceinline__ void acquire() {
         mbar_wait(empty_addr + cur.stage * 8, cur.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
     }
-    // one stage of `n` row granules (rows g*8.., one box each) at K offset kx
-    __device__ __forceinline__ void rows_stage(const CUtensorMap* tm, int kx, int g0, int n) {
+    // n consecutive granules starting at granule g0, K offset kx, into consecutive slots at dst:
+    // 64-row boxes, then 32-row boxes, then 8-row boxes
+    __device__ __forceinline__ void issue_run(const WeightMaps* tm, int kx, int g0, int n, uint32_t dst, uint32_t bar) {
+        int w = 0;
+        for (; w + 8 <= n; w += 8) tma_load_2d(dst + w * SLOT_BYTES, &tm->r64, kx, (g0 + w) * GRAN, bar, policy);
+        for (; w + 4 <= n; w += 4) tma_load_2d(dst + w * SLOT_BYTES, &tm->r32, kx, (g0 + w) * GRAN, bar, policy);
+        for (; w < n; ++w) tma_load_2d(dst + w * SLOT_BYTES, &tm->r8, kx, (g0 + w) * GRAN, bar, policy);
+    }
+    // one stage of `n` row granules (rows g0*8 ...) at K offset kx
+    __device__ __forceinline__ void rows_stage(const WeightMaps* tm, int kx, int g0, int n) {
         acquire();
         if (*ab.flag) return;
         const uint32_t bar = full_addr + cur.stage * 8;
         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
-        const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
-        for (int w = 0; w < n; ++w) tma_load_2d(dst + w * SLOT_BYTES, tm, kx, (g0 + w) * GRAN, bar, policy);
+        issue_run(tm, kx, g0, n, ring_addr + cur.stage * STAGE_BYTES, bar);
         cur.advance();
         ++issued;
     }
     // all stages of a row-partitioned GEMV: granules [g0, g0+cnt) of `tm`, KC chunks each
-    __device__ __forceinline__ void rows_phase(const CUtensorMap* tm, int g0, int cnt, int KC) {
+    __device__ __forceinline__ void rows_phase(const WeightMaps* tm, int g0, int cnt, int KC) {
         if (cnt <= 0) return;
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = g0;
         for (int r = 0; r < nr; ++r) {
             const int n = base + (r < extra ? 1 : 0);
             for (int c = 0; c < KC; ++c) rows_stage(tm, c * KCHUNK, g, n);
+            g += n;
+        }
+    }
+    // Two matrices streamed as ONE sequence of granules (A's cntA granules first, then B's), cut
+    // into rounds together, so that a CTA holding a bit of both still runs full-size stages.
+    __device__ __forceinline__ void rows_phase2(const WeightMaps* tmA, int gA0, int cntA, const WeightMaps* tmB, int gB0,
+                                                int cntB, int KC) {
+        const int cnt = cntA + cntB;
+        if (cnt <= 0) return;
+        const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
+        int g = 0;
+        for (int r = 0; r < nr; ++r) {
+            const int n = base + (r < extra ? 1 : 0);
+            const int nA = max(0, min(cntA - g, n));  // granules of this round that belong to A
+            for (int c = 0; c < KC; ++c) {
+                acquire();
+                if (*ab.flag) return;
+                const uint32_t bar = full_addr + cur.stage * 8;
+                mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
+                const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
+                if (nA > 0) issue_run(tmA, c * KCHUNK, gA0 + g, nA, dst, bar);
+                if (n > nA) issue_run(tmB, c * KCHUNK, gB0 + g + nA - cntA, n - nA, dst + nA * SLOT_BYTES, bar);
+                cur.advance();
+                ++issued;
+            }
             g += n;
         }
     }
@@ -600,6 +744,57 @@ struct Consumer {
             g += n;
         }
     }
+    // Mirror of Producer::rows_phase2.  Granule v < cntA multiplies xsA and reports to epiA(v, row,
+    // dot), the others xsB / epiB(v - cntA, ...).  after_a() runs once, by all consumer threads,
+    // right after the round that finishes A's last granule (at once when cntA == 0).
+    template <class EpiA, class EpiB, class AfterA>
+    __device__ __forceinline__ void rows_phase2(int cntA, int cntB, int KC, const float* xsA, const float* xsB, EpiA epiA,
+                                                EpiB epiB, AfterA after_a) {
+        const int cnt = cntA + cntB;
+        bool a_done = false;
+        if (cntA == 0) {
+            after_a();
+            a_done = true;
+        }
+        if (cnt <= 0) return;
+        const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
+        int g = 0;
+        for (int r = 0; r < nr; ++r) {
+            const int n = base + (r < extra ? 1 : 0);
+            const int v0 = g + warp, v1 = g + warp + NCWARP;
+            const bool a0 = warp < n, a1 = warp + NCWARP < n;
+            const float* x0 = (v0 < cntA) ? xsA : xsB;
+            const float* x1 = (v1 < cntA) ? xsA : xsB;
+            float acc0[GRAN], acc1[GRAN];
+#pragma unroll
+            for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
+            for (int c = 0; c < KC; ++c) {
+                const uint8_t* st = wait_stage();
+                if (a0) gemv_slot(st + warp * SLOT_BYTES, x0 + c * KCHUNK, lane, acc0);
+                if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, x1 + c * KCHUNK, lane, acc1);
+                release_stage();
+            }
+            if (a0) {
+                const float v = warp_reduce8(acc0, lane);
+                if ((lane & 3) == 0) {
+                    if (v0 < cntA) epiA(v0, reduce8_row(lane), v);
+                    else epiB(v0 - cntA, reduce8_row(lane), v);
+                }
+            }
+            if (a1) {
+                const float v = warp_reduce8(acc1, lane);
+                if ((lane & 3) == 0) {
+                    if (v1 < cntA) epiA(v1, reduce8_row(lane), v);
+                    else epiB(v1 - cntA, reduce8_row(lane), v);
+                }
+            }
+            g += n;
+            if (!a_done && g >= cntA) {
+                after_a();
+                a_done = true;
+            }
+        }
+    }
 };
 
 // ---------------------------------------------------------------- the kernel
@@ -647,17 +842,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     // ---- static work split (identical on producer and consumer side)
     const int KC1 = ceil_div(H, KCHUNK);
     const int NGq = (3 * KVW) / GRAN, NGu = F / GRAN, NG1 = NGq + NGu;
-    // CTAs [0, Gq) share the QKV rows, CTAs [Gq, G) the MLP-up rows, in proportion to
-    // their sizes, so no CTA needs both LayerNorms or a ragged extra round.
-    int Gq = (NGu == 0) ? G : (NGq == 0 ? 0 : static_cast<int>((static_cast<long long>(G) * NGq + NG1 / 2) / NG1));
-    if (NGq > 0 && NGu > 0) Gq = max(1, min(G - 1, Gq));
+    // Every CTA streams a share of the QKV rows first and a share of the MLP-up rows after it, as
+    // one sequence of granules.  The up share is cut so that QKV + up together are as even as the
+    // grid allows (p1_joint, verified by the host); otherwise each is split evenly on its own.
     int qa = 0, qb = 0, ua = 0, ub = 0;  // QKV granules [qa, qb), up granules [ua, ub)
-    if (cta < Gq) {
-        qa = part_begin(cta, NGq, Gq);
-        qb = part_begin(cta + 1, NGq, Gq);
+    if (p.p1_joint == 2) {
+        // grouped: CTAs [0, Gq) share the QKV rows, CTAs [Gq, G) the MLP-up rows
+        int Gq = (NGu == 0) ? G : (NGq == 0 ? 0 : static_cast<int>((static_cast<long long>(G) * NGq + NG1 / 2) / NG1));
+        if (NGq > 0 && NGu > 0) Gq = max(1, min(G - 1, Gq));
+        if (cta < Gq) {
+            qa = part_begin(cta, NGq, Gq);
+            qb = part_begin(cta + 1, NGq, Gq);
+        } else {
+            ua = part_begin(cta - Gq, NGu, G - Gq);
+            ub = part_begin(cta - Gq + 1, NGu, G - Gq);
+        }
     } else {
-        ua = part_begin(cta - Gq, NGu, G - Gq);
-        ub = part_begin(cta - Gq + 1, NGu, G - Gq);
+        qa = part_begin(cta, NGq, G);
+        qb = part_begin(cta + 1, NGq, G);
+        if (p.p1_joint == 1) {
+            ua = part_begin(cta, NG1, G) - qa;
+            ub = part_begin(cta + 1, NG1, G) - qb;
+        } else {
+            ua = part_begin(cta, NGu, G);
+            ub = part_begin(cta + 1, NGu, G);
+        }
     }
     const int nch = ceil_div(seq, KV_TILE);
     const int T2 = NH * nch;
@@ -696,8 +905,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             for (int l = 0; l < p.n_layers; ++l) {
                 const LayerDesc* L = p.layers + l;
                 if (p.phase_mask & PH_P1) {
-                    pr.rows_phase(&L->tm_qkv, qa, qb - qa, KC1);
-                    pr.rows_phase(&L->tm_up, ua, ub - ua, KC1);
+                    pr.rows_phase2(&L->tm_qkv, qa, qb - qa, &L->tm_up, ua, ub - ua, KC1);
                     trace_mark(p, cta, l, TR_PROD_P1);
                 }
                 if (p.phase_mask & PH_P2) {
@@ -897,6 +1105,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         const float* sinr = p.sin + pos_off;
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
         bool need_barrier = false;  // a phase of this launch wrote data the next one reads
+        bool arrived = false;       // counted in at a split barrier that has not been waited for yet
         // epochs of this launch's exchanges: launch count * (layers + 2) + layer + 1; never 0
         const unsigned tp_base = (p.tp_size > 1) ? __ldcg(p.tp_launch_count) * static_cast<unsigned>(p.n_layers + 2) : 0u;
 
@@ -918,45 +1127,48 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         p.trace[(static_cast<size_t>(cta) * (p.n_layers + 1) + l) * TRACE_EVENTS + 9] = smid;
                     }
                 }
-                bool have_stats = false;
-                if (qb > qa) {
-                    if (p.arch_flags & AF_RMS_ADD) {
-                        rms_norm_add_to_smem(x, p.residual_in, L->ln_w, H, p.norm_eps, sm.xbuf,
-                                             cta == 0 ? p.residual_out : nullptr, sm.red, tid);
-                    } else {
-                        layer_norm_to_smem(x, L->ln_w, L->ln_b, H, sm.xbuf, sm.red, tid, have_stats);
-                    }
-                    have_stats = true;
-                    if (tid == 0) trace_mark(p, cta, l, TR_LN_DONE);
-                    const __half* bq = L->b_qkv;
-                    float* dst = p.qkv_f32;
-                    const int row0 = qa * GRAN;
-                    co.rows_phase(qb - qa, KC1, sm.xbuf, [&](int g, int r, float v) {
-                        const int row = row0 + g * GRAN + r;
-                        const float out = bq ? v + __half2float(__ldg(bq + row)) : v;
-                        if (p.arch_flags & AF_QKV_PLANAR) {
-                            // row of [Q_all; K_all; V_all] -> slot of the per-head [q; k; v] scratch
-                            const int part = row / KVW, rem = row - part * KVW;
-                            const int h = rem / D;
-                            dst[h * 3 * D + part * D + (rem - h * D)] = out;
-                        } else {
-                            dst[row] = out;
-                        }
-                    });
-                    consumer_sync(NCTHR);  // xbuf is rewritten next
+                // both norms in one pass: y1 in xbuf[0, H), y2 in xbuf[H, 2H)
+                if (p.arch_flags & AF_RMS_ADD) {
+                    rms_norm_add_to_smem(x, p.residual_in, L->ln_w, H, p.norm_eps, sm.xbuf,
+                                         cta == 0 ? p.residual_out : nullptr, sm.red, tid);
+                } else {
+                    layer_norm2_to_smem(x, L->ln_w, L->ln_b, L->pln_w, L->pln_b, H, sm.xbuf,
+                                        (ub > ua) ? sm.xbuf + H : nullptr, sm.red, tid);
                 }
-                if (ub > ua) {
-                    layer_norm_to_smem(x, L->pln_w, L->pln_b, H, sm.xbuf, sm.red, tid, have_stats);
+                if (tid == 0) trace_mark(p, cta, l, TR_LN_DONE);
+                {
+                    const __half* bq = L->b_qkv;
                     const __half* bu = L->b_up;
-                    float* dst = p.mid_f32;
-                    __half* dst16 = p.mid_f16_out;
-                    const int row0 = ua * GRAN;
-                    co.rows_phase(ub - ua, KC1, sm.xbuf, [&](int g, int r, float v) {
-                        const int row = row0 + g * GRAN + r;
-                        const float a = gelu_tanh_f(v + __half2float(__ldg(bu + row)));
-                        dst[row] = a;
-                        if (dst16) dst16[row] = __float2half_rn(a);
-                    });
+                    float* dq = p.qkv_f32;
+                    float* dm = p.mid_f32;
+                    __half* dm16 = p.mid_f16_out;
+                    const int rowq0 = qa * GRAN, rowu0 = ua * GRAN;
+                    co.rows_phase2(
+                        qb - qa, ub - ua, KC1, sm.xbuf, sm.xbuf + H,
+                        [&](int g, int r, float v) {
+                            const int row = rowq0 + g * GRAN + r;
+                            const float out = bq ? v + __half2float(__ldg(bq + row)) : v;
+                            if (p.arch_flags & AF_QKV_PLANAR) {
+                                // row of [Q_all; K_all; V_all] -> slot of the per-head [q; k; v] scratch
+                                const int part = row / KVW, rem = row - part * KVW;
+                                const int h = rem / D;
+                                dq[h * 3 * D + part * D + (rem - h * D)] = out;
+                            } else {
+                                dq[row] = out;
+                            }
+                        },
+                        [&](int g, int r, float v) {
+                            const int row = rowu0 + g * GRAN + r;
+                            const float a = gelu_tanh_f(v + __half2float(__ldg(bu + row)));
+                            dm[row] = a;
+                            if (dm16) dm16[row] = __float2half_rn(a);
+                        },
+                        [&]() {
+                            // Attention needs every CTA's q/k/v: count in at the barrier as soon as this
+                            // CTA's QKV rows are out, wait for it only after its MLP-up rows.
+                            grid_arrive(p.sync, epoch, tid);
+                            arrived = true;
+                        });
                 }
                 if (tid == 0) trace_mark(p, cta, l, TR_P1_DONE);
                 need_barrier = true;
@@ -964,7 +1176,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
             // ------------------------------------------------------------ P2
             if (p.phase_mask & PH_P2) {
-                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                if (arrived) {
+                    grid_wait(p.sync, epoch, G, tid, ab);
+                    arrived = false;
+                } else if (need_barrier) {
+                    grid_barrier(p.sync, epoch, G, tid, ab);
+                }
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR1);
                 // Empty cache (seq == 0): there are no items, so the head's owner CTA turns the
                 // new token into the head's only partial.  Otherwise the CTA that streams the
@@ -1164,6 +1381,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
             // ------------------------------------------------------------ P3
             if (p.phase_mask & PH_P3) {
+                if (arrived) {  // P1 without P2 in this launch
+                    grid_wait(p.sync, epoch, G, tid, ab);
+                    arrived = false;
+                }
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR2);
                 // ---- this CTA's K slice of [mid ; attn] as fp32 in xbuf, chunk-major, MLP chunks
