@@ -32,7 +32,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "Pythia-6.9B B=1 decode TPOT (us) at 4K context"
+METRIC = "Pythia-6.9B B=1 decode TPOT (us) at 4K context"  # the default workload; other --model / --ctx are labelled below
 FALLBACK_HBM_GBS = 6650.0
 
 SHAPES = {  # hidden, heads, head_dim, rotary, ffn, vocab
@@ -286,8 +286,9 @@ def run_ours(args, rank, world):
     traffic = None
     if tp == 1 and args.model == "6b9" and args.ctx == 4096 and args.layers == 32:
         traffic = NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K
+    metric = METRIC if (args.model == "6b9" and args.ctx == 4096) else f"Pythia-{args.model} B=1 decode TPOT (us) at {args.ctx} context"
     line = {
-        "metric": METRIC, "value": tpot_us, "unit": "us/token", "n_gpus": tp, "steps": K, "warmup": W,
+        "metric": metric, "value": tpot_us, "unit": "us/token", "n_gpus": tp, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp16 (fp32 accumulate)", "data": "synthetic", "config": workload_config(args, tp),
         "clocks": clocks,

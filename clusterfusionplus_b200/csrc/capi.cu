@@ -333,8 +333,18 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         // the CTAs by matrix is ~0.4 % faster; with short ones (Pythia-2.8B, tensor-parallel shards) hiding
         // the barrier behind the MLP-up rows wins ~2 %.
         p.p1_joint = (ng1 / c.grid >= 20) ? 2 : (ok ? 1 : 0);
+        // Grouped split: MLP-up CTAs count in at barrier 1 before they start (attention needs only q/k/v), so
+        // the barrier waits for the QKV group alone.  Give that group one granule per CTA less than the
+        // average: it finishes a barrier latency early and nobody waits.
+        {
+            const int avg = ng1 / c.grid;
+            int gq = (avg > 1) ? ceil_div(ngq, avg - 1) : c.grid / 2;
+            const int forced = env_int("CFB200_GQ", 0);
+            if (forced > 0) gq = forced;
+            p.gq = gq;
+        }
         const int mode = env_int("CFB200_P1_MODE", -1);
-        if (mode == 0 || mode == 2 || (mode == 1 && ok)) p.p1_joint = mode;
+        if (mode == 0 || mode == 2 || mode == 3 || (mode == 1 && ok)) p.p1_joint = mode;
     }
     rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats);
     if (rc != CF_OK) return rc;

@@ -145,6 +145,7 @@ struct Params {
     int vocab_offset;  // added to the argmax index (vocabulary shards)
     int p1_joint;      // P1 row split: 1 = every CTA QKV share then up share, jointly balanced (host verified it
                        // is monotone), 0 = the same with independent even splits, 2 = grouped (QKV CTAs, up CTAs)
+    int gq;            // grouped split: CTAs in the QKV group
     int arch_flags;    // AF_*
     float norm_eps;    // RMSNorm epsilon (AF_RMS_ADD)
     const __half* residual_in;  // [H], AF_RMS_ADD
@@ -846,16 +847,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     // one sequence of granules.  The up share is cut so that QKV + up together are as even as the
     // grid allows (p1_joint, verified by the host); otherwise each is split evenly on its own.
     int qa = 0, qb = 0, ua = 0, ub = 0;  // QKV granules [qa, qb), up granules [ua, ub)
-    if (p.p1_joint == 2) {
+    if (p.p1_joint >= 2) {
         // grouped: CTAs [0, Gq) share the QKV rows, CTAs [Gq, G) the MLP-up rows
-        int Gq = (NGu == 0) ? G : (NGq == 0 ? 0 : static_cast<int>((static_cast<long long>(G) * NGq + NG1 / 2) / NG1));
+        int Gq = (NGu == 0) ? G : (NGq == 0 ? 0 : p.gq);
         if (NGq > 0 && NGu > 0) Gq = max(1, min(G - 1, Gq));
-        if (cta < Gq) {
-            qa = part_begin(cta, NGq, Gq);
-            qb = part_begin(cta + 1, NGq, Gq);
+        const int vc = (p.p1_joint == 3) ? G - 1 - cta : cta;
+        if (vc < Gq) {
+            qa = part_begin(vc, NGq, Gq);
+            qb = part_begin(vc + 1, NGq, Gq);
         } else {
-            ua = part_begin(cta - Gq, NGu, G - Gq);
-            ub = part_begin(cta - Gq + 1, NGu, G - Gq);
+            ua = part_begin(vc - Gq, NGu, G - Gq);
+            ub = part_begin(vc - Gq + 1, NGu, G - Gq);
         }
     } else {
         qa = part_begin(cta, NGq, G);
