@@ -329,16 +329,19 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
             ok = u >= prev;
             prev = u;
         }
-        // Measured on B200: with long P1 streams (>= 20 granules per CTA: Pythia-6.9B on one GPU) grouping
-        // the CTAs by matrix is ~0.4 % faster; with short ones (Pythia-2.8B, tensor-parallel shards) hiding
-        // the barrier behind the MLP-up rows wins ~2 %.
-        p.p1_joint = (ng1 / c.grid >= 20) ? 2 : (ok ? 1 : 0);
+        // Measured on B200: grouping the CTAs by matrix beats giving every CTA both matrices for
+        // Pythia-6.9B on 1, 4 and 8 GPUs (0.4 - 6 %), ties on 2 GPUs, loses 1.5 % for Pythia-2.8B.
+        p.p1_joint = 2;  // grouped; 1 / 0 (every CTA both matrices) stay selectable for experiments
+        (void)ok;
         // Grouped split: MLP-up CTAs count in at barrier 1 before they start (attention needs only q/k/v), so
         // the barrier waits for the QKV group alone.  Give that group one granule per CTA less than the
         // average: it finishes a barrier latency early and nobody waits.
         {
-            const int avg = ng1 / c.grid;
-            int gq = (avg > 1) ? ceil_div(ngq, avg - 1) : c.grid / 2;
+            // ... but never more than 10 % less, which matters for small shards
+            const double avg = static_cast<double>(ng1) / c.grid;
+            const double per_q = (avg - 1.0 > 0.9 * avg) ? avg - 1.0 : 0.9 * avg;
+            int gq = (ngq > 0 && ng1 > ngq) ? static_cast<int>(ngq / per_q + 0.999) : c.grid;
+            if (gq < 1) gq = 1;
             const int forced = env_int("CFB200_GQ", 0);
             if (forced > 0) gq = forced;
             p.gq = gq;
