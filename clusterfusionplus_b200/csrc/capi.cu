@@ -96,7 +96,8 @@ int encode_weight(WeightMaps* m, const void* ptr, uint64_t cols, uint64_t rows) 
 
 struct Workspace {
     void* base = nullptr;
-    float *qkv_f32 = nullptr, *mid_f32 = nullptr, *attn_part = nullptr, *attn_new = nullptr, *amax_val = nullptr;
+    uint2* qkv_ll = nullptr;
+    float *mid_f32 = nullptr, *attn_part = nullptr, *attn_new = nullptr, *amax_val = nullptr;
     int* amax_idx = nullptr;
     unsigned* sync = nullptr;
     int* status = nullptr;
@@ -116,7 +117,7 @@ int ws_alloc(Workspace& w) {
         off = align_up(off + bytes, 256);
         return o;
     };
-    const size_t o_qkv = take(sizeof(float) * WS_MAX_QKV);
+    const size_t o_qkv = take(sizeof(uint2) * WS_MAX_QKV);
     const size_t o_mid = take(sizeof(float) * WS_MAX_F);
     const size_t o_part = take(sizeof(float) * WS_MAX_GRID * MAXL * (128 + 4));
     const size_t o_new = take(sizeof(float) * WS_MAX_HEADS * (128 + 4));
@@ -128,7 +129,7 @@ int ws_alloc(Workspace& w) {
     CF_CUDA(cudaMalloc(&b, off));
     CF_CUDA(cudaMemset(b, 0, off));
     w.base = b;
-    w.qkv_f32 = reinterpret_cast<float*>(b + o_qkv);
+    w.qkv_ll = reinterpret_cast<uint2*>(b + o_qkv);
     w.mid_f32 = reinterpret_cast<float*>(b + o_mid);
     w.attn_part = reinterpret_cast<float*>(b + o_part);
     w.attn_new = reinterpret_cast<float*>(b + o_new);
@@ -197,7 +198,10 @@ int env_int(const char* name, int dflt) {
     return (v && *v) ? atoi(v) : dflt;
 }
 
+std::mutex g_cfg_mu;  // launch geometry is chosen once per (device, head_dim); serialise the choosing
+
 int pick_cfg(DeviceState& ds, int D) {
+    std::lock_guard<std::mutex> lk(g_cfg_mu);
     LaunchCfg& c = ds.cfg[D == 128];
     if (c.ready) return CF_OK;
     const int forced = env_int("CFB200_CLUSTER", 0);
@@ -353,6 +357,7 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     if (rc != CF_OK) return rc;
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
     const void* fn = kernel_ptr(d.head_dim, c.cs);
+    p.qkv_any_epoch = (p.phase_mask & PH_P1) ? 0 : 1;
     p.trace = nullptr;
     if (ds.trace && static_cast<size_t>(c.grid) * (p.n_layers + 1) * TRACE_EVENTS <= ds.trace_slots) p.trace = ds.trace;
     for (int attempt = 0; attempt < 2; ++attempt) {
@@ -399,7 +404,8 @@ void base_params(Params& p, const CfDims& d, const Workspace& ws) {
     p.NH = d.heads;
     p.R = d.rotary;
     p.F = d.ffn;
-    p.qkv_f32 = ws.qkv_f32;
+    p.qkv_ll = ws.qkv_ll;
+    p.launch_count = ws.sync + 2;
     p.mid_f32 = ws.mid_f32;
     p.attn_part = ws.attn_part;
     p.attn_new = ws.attn_new;
@@ -610,7 +616,7 @@ constexpr int NOALLOC_MAX_HEADS = 32;
 constexpr int NOALLOC_MAX_KVW = 4096;   // heads * head_dim
 constexpr int NOALLOC_MAX_FFN = 16384;
 constexpr size_t NA_OFF_QKV = 0;
-constexpr size_t NA_OFF_MID = NA_OFF_QKV + sizeof(float) * 3 * NOALLOC_MAX_KVW;
+constexpr size_t NA_OFF_MID = NA_OFF_QKV + sizeof(uint2) * 3 * NOALLOC_MAX_KVW;
 constexpr size_t NA_OFF_PART = NA_OFF_MID + sizeof(float) * NOALLOC_MAX_FFN;
 constexpr size_t NA_OFF_NEW = NA_OFF_PART + sizeof(float) * NOALLOC_MAX_GRID * MAXL * (128 + 4);
 constexpr size_t NA_OFF_AMAXV = NA_OFF_NEW + sizeof(float) * NOALLOC_MAX_HEADS * (128 + 4);
@@ -618,7 +624,7 @@ constexpr size_t NA_OFF_AMAXI = NA_OFF_AMAXV + sizeof(float) * NOALLOC_MAX_GRID;
 constexpr size_t NA_OFF_SYNC = NA_OFF_AMAXI + sizeof(int) * NOALLOC_MAX_GRID;   // 4 barrier words + 4 status words
 constexpr size_t NA_OFF_DESC = (NA_OFF_SYNC + 32 + 255) / 256 * 256;            // one LayerDesc (tensor maps)
 constexpr size_t NOALLOC_SCRATCH_BYTES = NA_OFF_DESC + sizeof(LayerDesc);
-static_assert(NOALLOC_SCRATCH_BYTES <= 512 * 1024, "the static scratch is meant to stay modest");
+static_assert(NOALLOC_SCRATCH_BYTES <= 576 * 1024, "the static scratch is meant to stay modest");
 static_assert(NA_OFF_MID % 256 == 0 && NA_OFF_PART % 256 == 0 && NA_OFF_NEW % 128 == 0 && NA_OFF_SYNC % 16 == 0,
               "sub-buffers must keep the alignment the kernel's vector loads and tensor maps need");
 
@@ -660,7 +666,7 @@ int noalloc_setup(NoAllocDevice** out) {
         nd.ds.smem_optin = optin;
         Workspace& w = nd.ds.ws;
         w.base = nd.scratch;
-        w.qkv_f32 = reinterpret_cast<float*>(nd.scratch + NA_OFF_QKV);
+        w.qkv_ll = reinterpret_cast<uint2*>(nd.scratch + NA_OFF_QKV);
         w.mid_f32 = reinterpret_cast<float*>(nd.scratch + NA_OFF_MID);
         w.attn_part = reinterpret_cast<float*>(nd.scratch + NA_OFF_PART);
         w.attn_new = reinterpret_cast<float*>(nd.scratch + NA_OFF_NEW);
@@ -717,7 +723,7 @@ int cf_get_status(int* status) {
         if (s != 0) {
             worst = s;
             CF_CUDA(cudaMemset(ws.status, 0, sizeof(int)));
-            CF_CUDA(cudaMemset(ws.sync, 0, 4 * sizeof(unsigned)));
+            CF_CUDA(cudaMemset(ws.sync, 0, 2 * sizeof(unsigned)));  // barrier words only: the launch count keeps counting
         }
         return CF_OK;
     };
@@ -760,7 +766,9 @@ int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const Cf
                     nd->ds.cfg[d.head_dim == 128].grid, NOALLOC_MAX_GRID);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // the array keeps whatever the last call left: barrier and status words must start at zero
-    CF_CUDA(cudaMemsetAsync(nd->ds.ws.sync, 0, 32, st));
+    // (the third sync word is the launch count behind the q/k/v epochs: it must keep counting)
+    CF_CUDA(cudaMemsetAsync(nd->ds.ws.sync, 0, 8, st));
+    CF_CUDA(cudaMemsetAsync(nd->ds.ws.status, 0, 4, st));
     // tensor maps + pointers of this call's tensors into the descriptor slot (a copy, not an allocation)
     DescKey key;
     memset(&key, 0, sizeof(key));

@@ -130,7 +130,9 @@ struct Params {
     const __half* mid_f16_in;     // with F3_MID_F16
     const __half* extra_add_f16;  // optional [H] added in the P3 epilogue
     // scratch
-    float* qkv_f32;    // [3*NH*D]
+    uint2* qkv_ll;     // [3*NH*D] {fp32 bits, epoch}: q/k/v rows travel with the epoch of their launch and layer
+    unsigned* launch_count;  // +1 per launch (last CTA out): makes those epochs unique
+    int qkv_any_epoch; // the launch has no P1: take whatever an earlier launch left in qkv_ll
     float* mid_f32;    // [F]
     float* attn_part;  // [grid][MAXL][D+4]: D numerators, max, denominator, 2 pad
     float* attn_new;   // [NH][D+4]
@@ -335,13 +337,27 @@ __device__ __forceinline__ float block_sum(float v, float* red, int tid) {
     return t;
 }
 
-// rotate-half RoPE on element d (< D) of a head vector held in global scratch
-__device__ __forceinline__ float rope_elem(const float* vec, int d, int R, const float* cosr, const float* sinr) {
-    const float v = ld_cg_f32(vec + d);
+// One q/k/v element from the scratch that P1 filled: wait (bounded) until its word carries this
+// layer's epoch.  There is no grid barrier between P1 and P2: a CTA starts on a head as soon
+// as that head's rows are there.
+struct QkvView {
+    const uint2* base;
+    unsigned epoch;
+    bool any;
+    const AbortCtl* ab;
+    __device__ __forceinline__ float get(int idx) const {
+        if (any) return __uint_as_float(ld_ll(base + idx).x);
+        return __uint_as_float(wait_ll(base + idx, epoch, *ab));
+    }
+};
+
+// rotate-half RoPE on element d (< D) of the head vector starting at scratch index i0
+__device__ __forceinline__ float rope_elem(const QkvView& q, int i0, int d, int R, const float* cosr, const float* sinr) {
+    const float v = q.get(i0 + d);
     if (d >= R) return v;
     const int half_r = R >> 1;
     const float c = __ldg(cosr + d), s = __ldg(sinr + d);
-    const float partner = (d < half_r) ? -ld_cg_f32(vec + d + half_r) : ld_cg_f32(vec + d - half_r);
+    const float partner = (d < half_r) ? -q.get(i0 + d + half_r) : q.get(i0 + d - half_r);
     return v * c + partner * s;
 }
 
@@ -1106,8 +1122,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         const float* cosr = p.cos + pos_off;
         const float* sinr = p.sin + pos_off;
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
+        // epochs of this launch's flag-in-data handoffs: launch count * (layers + 2) + layer + 1; never 0
+        const unsigned ll_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
         bool need_barrier = false;  // a phase of this launch wrote data the next one reads
-        bool arrived = false;       // counted in at a split barrier that has not been waited for yet
         // epochs of this launch's exchanges: launch count * (layers + 2) + layer + 1; never 0
         const unsigned tp_base = (p.tp_size > 1) ? __ldcg(p.tp_launch_count) * static_cast<unsigned>(p.n_layers + 2) : 0u;
 
@@ -1141,7 +1158,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 {
                     const __half* bq = L->b_qkv;
                     const __half* bu = L->b_up;
-                    float* dq = p.qkv_f32;
+                    uint2* dq = p.qkv_ll;
+                    const unsigned qep = ll_base + static_cast<unsigned>(l) + 1u;
                     float* dm = p.mid_f32;
                     __half* dm16 = p.mid_f16_out;
                     const int rowq0 = qa * GRAN, rowu0 = ua * GRAN;
@@ -1154,9 +1172,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                                 // row of [Q_all; K_all; V_all] -> slot of the per-head [q; k; v] scratch
                                 const int part = row / KVW, rem = row - part * KVW;
                                 const int h = rem / D;
-                                dq[h * 3 * D + part * D + (rem - h * D)] = out;
+                                st_ll(dq + h * 3 * D + part * D + (rem - h * D), __float_as_uint(out), qep);
                             } else {
-                                dq[row] = out;
+                                st_ll(dq + row, __float_as_uint(out), qep);
                             }
                         },
                         [&](int g, int r, float v) {
@@ -1165,12 +1183,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             dm[row] = a;
                             if (dm16) dm16[row] = __float2half_rn(a);
                         },
-                        [&]() {
-                            // Attention needs every CTA's q/k/v: count in at the barrier as soon as this
-                            // CTA's QKV rows are out, wait for it only after its MLP-up rows.
-                            grid_arrive(p.sync, epoch, tid);
-                            arrived = true;
-                        });
+                        [&]() {});
                 }
                 if (tid == 0) trace_mark(p, cta, l, TR_P1_DONE);
                 need_barrier = true;
@@ -1178,12 +1191,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
             // ------------------------------------------------------------ P2
             if (p.phase_mask & PH_P2) {
-                if (arrived) {
-                    grid_wait(p.sync, epoch, G, tid, ab);
-                    arrived = false;
-                } else if (need_barrier) {
-                    grid_barrier(p.sync, epoch, G, tid, ab);
-                }
+                // no grid barrier here: q/k/v words carry their epoch and are polled where they are used
+                const QkvView qkv{p.qkv_ll, ll_base + static_cast<unsigned>(l) + 1u, p.qkv_any_epoch != 0, &ab};
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR1);
                 // Empty cache (seq == 0): there are no items, so the head's owner CTA turns the
                 // new token into the head's only partial.  Otherwise the CTA that streams the
@@ -1191,12 +1200,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (nch == 0 && warp == 0) {
                     for (int h = 0; h < NH; ++h) {
                         if (head_owner(h, NH, G) != cta) continue;
-                        const float* qv = p.qkv_f32 + h * 3 * D;
+                        const int qi = h * 3 * D;
                         float s = 0.f;
                         for (int d = lane; d < D; d += 32) {
-                            const float qd = rope_elem(qv, d, R, cosr, sinr) * qscale;
-                            const __half k16 = __float2half_rn(rope_elem(qv + D, d, R, cosr, sinr));
-                            const __half v16 = __float2half_rn(ld_cg_f32(qv + 2 * D + d));
+                            const float qd = rope_elem(qkv, qi, d, R, cosr, sinr) * qscale;
+                            const __half k16 = __float2half_rn(rope_elem(qkv, qi + D, d, R, cosr, sinr));
+                            const __half v16 = __float2half_rn(qkv.get(qi + 2 * D + d));
                             s = fmaf(qd, __half2float(k16), s);
                             const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
                             if (!(p.arch_flags & AF_NO_APPEND)) {
@@ -1266,14 +1275,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         // q for every CTA on this head; k, v (fp16-rounded, appended to the
                         // cache) only where the head's last chunk is streamed
                         const bool has_last = (h + 1) * nch - 1 < t2b;
-                        const float* qv = p.qkv_f32 + h * 3 * D;
+                        const int qi = h * 3 * D;
                         for (int e = tid; e < (has_last ? 3 * D : D); e += NCTHR) {
                             const int part = e / D, d = e - part * D;
                             if (part == 0) {
-                                sm.q_s[d] = rope_elem(qv, d, R, cosr, sinr) * qscale;
+                                sm.q_s[d] = rope_elem(qkv, qi, d, R, cosr, sinr) * qscale;
                             } else {
-                                const float val = (part == 1) ? rope_elem(qv + D, d, R, cosr, sinr)
-                                                              : ld_cg_f32(qv + 2 * D + d);
+                                const float val = (part == 1) ? rope_elem(qkv, qi + D, d, R, cosr, sinr)
+                                                              : qkv.get(qi + 2 * D + d);
                                 const __half h16 = __float2half_rn(val);
                                 sm.kv_s[(part - 1) * D + d] = __half2float(h16);
                                 const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
@@ -1383,10 +1392,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
             // ------------------------------------------------------------ P3
             if (p.phase_mask & PH_P3) {
-                if (arrived) {  // P1 without P2 in this launch
-                    grid_wait(p.sync, epoch, G, tid, ab);
-                    arrived = false;
-                }
                 if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR2);
                 // ---- this CTA's K slice of [mid ; attn] as fp32 in xbuf, chunk-major, MLP chunks
@@ -1607,7 +1612,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         }
 
         // ---- leave: count out; the last CTA re-arms the barrier words
-        if (epoch > 0 || p.seq_inc) {
+        {
             consumer_sync(NCTHR);
             if (tid == 0) {
                 __threadfence();
@@ -1615,6 +1620,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (old == static_cast<unsigned>(G) - 1u) {
                     p.sync[0] = 0u;
                     p.sync[1] = 0u;
+                    *p.launch_count = *p.launch_count + 1u;
                     if (p.seq_inc) *p.seq_inc = seq + 1;
                     if (p.tp_size > 1) *p.tp_launch_count = *p.tp_launch_count + 1u;
                     __threadfence();
