@@ -97,6 +97,7 @@ int encode_weight(WeightMaps* m, const void* ptr, uint64_t cols, uint64_t rows) 
 struct Workspace {
     void* base = nullptr;
     uint2* qkv_ll = nullptr;
+    uint2* hid_ll[2] = {nullptr, nullptr};
     float *mid_f32 = nullptr, *attn_part = nullptr, *attn_new = nullptr, *amax_val = nullptr;
     int* amax_idx = nullptr;
     unsigned* sync = nullptr;
@@ -119,6 +120,8 @@ int ws_alloc(Workspace& w) {
     };
     const size_t o_qkv = take(sizeof(uint2) * WS_MAX_QKV);
     const size_t o_mid = take(sizeof(float) * WS_MAX_F);
+    const size_t o_hid0 = take(sizeof(uint2) * MAX_H);
+    const size_t o_hid1 = take(sizeof(uint2) * MAX_H);
     const size_t o_part = take(sizeof(float) * WS_MAX_GRID * MAXL * (128 + 4));
     const size_t o_new = take(sizeof(float) * WS_MAX_HEADS * (128 + 4));
     const size_t o_av = take(sizeof(float) * WS_MAX_GRID);
@@ -131,6 +134,8 @@ int ws_alloc(Workspace& w) {
     w.base = b;
     w.qkv_ll = reinterpret_cast<uint2*>(b + o_qkv);
     w.mid_f32 = reinterpret_cast<float*>(b + o_mid);
+    w.hid_ll[0] = reinterpret_cast<uint2*>(b + o_hid0);
+    w.hid_ll[1] = reinterpret_cast<uint2*>(b + o_hid1);
     w.attn_part = reinterpret_cast<float*>(b + o_part);
     w.attn_new = reinterpret_cast<float*>(b + o_new);
     w.amax_val = reinterpret_cast<float*>(b + o_av);
@@ -406,6 +411,8 @@ void base_params(Params& p, const CfDims& d, const Workspace& ws) {
     p.F = d.ffn;
     p.qkv_ll = ws.qkv_ll;
     p.launch_count = ws.sync + 2;
+    p.hid_ll[0] = ws.hid_ll[0];
+    p.hid_ll[1] = ws.hid_ll[1];
     p.mid_f32 = ws.mid_f32;
     p.attn_part = ws.attn_part;
     p.attn_new = ws.attn_new;
@@ -602,8 +609,6 @@ void decoder_params(Decoder& dc, Params& p) {
     p.sin = dc.cfg.sin_table;
     p.rope_stride = dc.cfg.dims.rotary;
     p.seq_ptr = dc.seq_d;
-    p.hid[0] = dc.hid0;
-    p.hid[1] = dc.hid1;
 }
 
 // ---------------------------------------------------------------------------

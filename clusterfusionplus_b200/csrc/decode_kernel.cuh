@@ -117,7 +117,7 @@ struct Params {
     const __half* embed;  // optional [V, H] table: x = embed[*token_in]
     const int* token_in;
     __half* out;          // output of the last layer of this launch
-    __half* hid[2];       // ping-pong hidden state between layers of one launch
+    uint2* hid_ll[2];     // hidden state between layers of one launch, ping-pong, {fp16 bits, epoch} per element
     __half* k_new;        // optional [NH*D] (single-layer launches)
     __half* v_new;
     const float* cos;     // row for this position, or table base when rope_stride > 0
@@ -179,6 +179,12 @@ __device__ __forceinline__ void st_ll(void* p, unsigned bits, unsigned epoch) {
 __device__ __forceinline__ uint2 ld_ll(const void* p) {
     uint2 v;
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// two adjacent words in one 16-byte load: {bits0, epoch0, bits1, epoch1}
+__device__ __forceinline__ uint4 ld_ll2(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
 // wait (bounded) until the word at p carries `epoch`; returns its payload bits
@@ -484,7 +490,11 @@ __device__ __forceinline__ void layer_norm_to_smem(const __half* x, const __half
 // LayerNorm of x[H] into out1 with (gamma1, beta1) and, when out2 != nullptr, into out2 with
 // (gamma2, beta2) from the same mean / rstd: the input norm and the post-attention norm of a
 // parallel-residual layer see the same input.  Two-pass statistics in fp32.
-__device__ __forceinline__ void layer_norm2_to_smem(const __half* x, const __half* gamma1, const __half* beta1,
+// The input is either plain fp16 (x) or, when xll != nullptr, the epoch-tagged words another
+// layer of this launch produced: they are polled (bounded) until every one carries `xep`,
+// which is what replaces a grid barrier between layers.
+__device__ __forceinline__ void layer_norm2_to_smem(const __half* x, const uint2* xll, unsigned xep, const AbortCtl& ab,
+                                                    const __half* gamma1, const __half* beta1,
                                                     const __half* gamma2, const __half* beta2, int H, float* out1,
                                                     float* out2, float* red, int tid) {
     constexpr int NV = MAX_H / (NCTHR * 8);
@@ -506,7 +516,25 @@ __device__ __forceinline__ void layer_norm2_to_smem(const __half* x, const __hal
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
         const int v = j * NCTHR + tid;
-        if (v < nvec) {
+        if (v < nvec && xll) {
+            uint4 w[4];
+            wait_bounded(
+                [&] {
+                    bool ok = true;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        w[q] = ld_ll2(xll + v * 8 + 2 * q);
+                        ok = ok && w[q].y == xep && w[q].w == xep;
+                    }
+                    return ok;
+                },
+                ab, ST_TIMEOUT_GRID);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                xv[j][2 * q] = __half2float(__ushort_as_half(static_cast<unsigned short>(w[q].x)));
+                xv[j][2 * q + 1] = __half2float(__ushort_as_half(static_cast<unsigned short>(w[q].z)));
+            }
+        } else if (v < nvec) {
             const uint4 raw = ld_cg_u32x4(x + v * 8);
             const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
@@ -1132,12 +1160,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
         for (int l = 0; l < p.n_layers; ++l) {
             const LayerDesc* L = p.layers + l;
-            const __half* x = (l == 0) ? x_first : p.hid[(l - 1) & 1];
-            __half* y = (l == p.n_layers - 1) ? p.out : p.hid[l & 1];
+            // layer input: the launch's input (plain fp16) or the previous layer's epoch-tagged words
+            const __half* x = (l == 0) ? x_first : nullptr;
+            const uint2* xll = (l == 0) ? nullptr : p.hid_ll[(l - 1) & 1];
+            const unsigned xep = ll_base + static_cast<unsigned>(l);  // = epoch of layer l - 1
+            // layer output: plain fp16 for the last layer of the launch, tagged words otherwise
+            __half* y = (l == p.n_layers - 1) ? p.out : nullptr;
+            uint2* yll = p.hid_ll[l & 1];
+            const unsigned yep = ll_base + static_cast<unsigned>(l) + 1u;
+            auto store_y = [&](int row, float v) {
+                const __half hv = __float2half_rn(v);
+                if (y) y[row] = hv;
+                else st_ll(yll + row, static_cast<unsigned>(__half_as_ushort(hv)), yep);
+            };
 
             // ------------------------------------------------------------ P1
             if (p.phase_mask & PH_P1) {
-                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                // no grid barrier between layers: the tagged input words are polled by the LayerNorm
                 if (tid == 0) {
                     trace_mark(p, cta, l, TR_START);
                     if (p.trace) {
@@ -1151,7 +1190,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     rms_norm_add_to_smem(x, p.residual_in, L->ln_w, H, p.norm_eps, sm.xbuf,
                                          cta == 0 ? p.residual_out : nullptr, sm.red, tid);
                 } else {
-                    layer_norm2_to_smem(x, L->ln_w, L->ln_b, L->pln_w, L->pln_b, H, sm.xbuf,
+                    layer_norm2_to_smem(x, xll, xep, ab, L->ln_w, L->ln_b, L->pln_w, L->pln_b, H, sm.xbuf,
                                         (ub > ua) ? sm.xbuf + H : nullptr, sm.red, tid);
                 }
                 if (tid == 0) trace_mark(p, cta, l, TR_LN_DONE);
@@ -1435,7 +1474,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         const int row = g3a * GRAN + me + tid * CS;
                         if (p.p3_flags & F3_ADD_BO) epi_add += __half2float(__ldg(L->b_o + row));
                         if (p.p3_flags & F3_ADD_BDOWN) epi_add += __half2float(__ldg(L->b_down + row));
-                        if (p.p3_flags & F3_ADD_X) epi_add += __half2float(ld_cg_f16(x + row));
+                        if (p.p3_flags & F3_ADD_X)
+                            epi_add += x ? __half2float(ld_cg_f16(x + row))
+                                         : __half2float(__ushort_as_half(static_cast<unsigned short>(ld_ll(xll + row).x)));
                         if (p.extra_add_f16) epi_add += __half2float(ld_cg_f16(p.extra_add_f16 + row));
                     }
                 }
@@ -1464,7 +1505,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (p.tp_size <= 1) {
                     if (me + tid * CS < nrows) {
                         const int row = g3a * GRAN + me + tid * CS;
-                        y[row] = __float2half_rn(dsm::tree_sum<CS>(sm.recv, stride, tid) + epi_add);
+                        store_y(row, dsm::tree_sum<CS>(sm.recv, stride, tid) + epi_add);
                     }
                 } else {
                     // Tensor parallel: what this CTA holds is one rank's partial of its rows.  The
@@ -1491,7 +1532,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                                 : __uint_as_float(wait_ll(p.tp_peer[p.tp_rank] + tl.partial_off(parity, r) + static_cast<size_t>(row) * 8, tp_epoch, ab));
                             sum += v;
                         }
-                        y[row] = __float2half_rn(sum + epi_add);
+                        store_y(row, sum + epi_add);
                     }
                 }
                 if (tid == 0) trace_mark(p, cta, l, TR_P3_DONE);

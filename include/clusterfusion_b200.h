@@ -106,7 +106,7 @@ int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLa
  * this entry point performs no cudaMalloc / cudaFree and calls no allocating routine:
  * its scratch (fp32 QKV and MLP intermediates, attention partials, barrier words and
  * the layer descriptor with its tensor maps) lives in a static __device__ array of
- * 472,960 bytes that every GPU loading the library holds until exit.
+ * 522,112 bytes that every GPU loading the library holds until exit.
  *   Limits: the built-in models only (at most 32 heads, 4096 QKV columns, ffn 16384)
  *   on at most 160 CTAs; anything larger is rejected with CF_ERR_UNSUPPORTED.
  *   The first call on a device looks up the array's device address and the launch
