@@ -363,6 +363,7 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
     const void* fn = kernel_ptr(d.head_dim, c.cs);
     p.qkv_any_epoch = (p.phase_mask & PH_P1) ? 0 : 1;
+    p.part_any_epoch = (p.phase_mask & PH_P2) ? 0 : 1;
     p.trace = nullptr;
     if (ds.trace && static_cast<size_t>(c.grid) * (p.n_layers + 1) * TRACE_EVENTS <= ds.trace_slots) p.trace = ds.trace;
     for (int attempt = 0; attempt < 2; ++attempt) {

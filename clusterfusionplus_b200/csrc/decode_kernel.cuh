@@ -134,9 +134,10 @@ struct Params {
     unsigned* launch_count;  // +1 per launch (last CTA out): makes those epochs unique
     int qkv_any_epoch; // the launch has no P1: take whatever an earlier launch left in qkv_ll
     float* mid_f32;    // [F]
-    float* attn_part;  // [grid][MAXL][D+4]: D numerators, max, denominator, 2 pad
-    float* attn_new;   // [NH][D+4]
-    unsigned* sync;    // [0] barrier count, [1] exit count
+    float* attn_part;  // [grid][MAXL][D+4]: D numerators, max, denominator, epoch (written last), 1 pad
+    float* attn_new;   // [NH][D+4], same record
+    int part_any_epoch;  // the launch has no P2: take the attention partials an earlier launch left
+    unsigned* sync;    // [0] barrier count, [1] exit count, [2] launch count, [3] CTAs past P1 (counts up over layers)
     int* status;
     // tail outputs
     float* logits;     // optional [vocab]
@@ -194,6 +195,14 @@ __device__ __forceinline__ unsigned wait_ll(const void* p, unsigned epoch, const
     return v.x;
 }
 
+// A record (attention partial) written with plain stores by several threads of the CTA, which
+// then met at a CTA barrier: one thread makes them visible device-wide and stamps the record's
+// epoch word.  A reader that acquires the epoch sees the record.
+__device__ __forceinline__ void publish_record(float* epoch_word, unsigned epoch) {
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(epoch_word), "r"(epoch) : "memory");
+}
+
 constexpr int TRACE_EVENTS = 16;
 enum : int {
     TR_START = 0, TR_LN_DONE, TR_P1_DONE, TR_BAR1, TR_P2_DONE, TR_BAR2, TR_X3_BUILT, TR_P3_GEMV, TR_P3_DONE,
@@ -243,12 +252,13 @@ struct Smem {
     uint64_t* xbar;
     uint64_t* h_go;        // consumers -> helpers: the barrier before P3 has been passed
     uint64_t* attn_ready;  // helpers -> consumers: merged attention chunks are in xbuf
+    uint64_t* mid_ready;   // helper thread -> consumers: every CTA is past P1, the MLP intermediate is complete
     int* abort_flag;
 };
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 3) * 8 + 16;
+           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 4) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -268,7 +278,8 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.xbar = s.empty + MAX_STAGES;
     s.h_go = s.xbar + 1;
     s.attn_ready = s.xbar + 2;
-    s.abort_flag = reinterpret_cast<int*>(s.xbar + 3);
+    s.mid_ready = s.xbar + 3;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 4);
     return s;
 }
 
@@ -864,6 +875,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         mbar_init(smem_u32(sm.xbar), CS > 1 ? CS - 1 : 1);
         mbar_init(smem_u32(sm.h_go), 1);
         mbar_init(smem_u32(sm.attn_ready), NHWARP);
+        mbar_init(smem_u32(sm.mid_ready), 1);
         mbar_fence_init();
     }
     __syncthreads();
@@ -1005,6 +1017,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         const int ht = tid - (NCWARP + 1) * 32;
         const int nmid = my3 - nattn;
         const int nent = nattn * HPC * pstr;
+        // every CTA past P1 <=> the MLP intermediate is complete: one helper thread watches the
+        // count and tells the consumers through shared memory, so that they never poll global memory
+        const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
+        auto watch_mid = [&](int l) {
+            if (mid_wait && ht == 0) {
+                const unsigned target = static_cast<unsigned>(l + 1) * static_cast<unsigned>(G);
+                wait_bounded([&] { return ld_acquire_u32(p.sync + 3) >= target; }, ab, ST_TIMEOUT_GRID);
+                __threadfence();
+                mbar_arrive(smem_u32(sm.mid_ready));
+            }
+        };
+        if ((p.phase_mask & PH_P3) && nattn == 0) {
+            for (int l = 0; l < p.n_layers; ++l) watch_mid(l);
+        }
         if ((p.phase_mask & PH_P3) && nattn > 0) {
             // Which partial feeds which of my chunks depends only on (grid, seq): tabulate once.
             for (int it = ht; it < nent; it += NHTHR) {
@@ -1031,9 +1057,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
             constexpr int ML_ITERS = (WTS_SLOTS + NHTHR - 1) / NHTHR;
             uint32_t gpar = 0;
+            const unsigned hl_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
             for (int l = 0; l < p.n_layers; ++l) {
+                watch_mid(l);
+                // the consumers have left P2 of this layer: xbuf's attention chunks are free
                 mbar_wait(smem_u32(sm.h_go), gpar, ab, ST_TIMEOUT_GRID);
                 gpar ^= 1u;
+                const unsigned pep = hl_base + static_cast<unsigned>(l) + 1u;
                 // (max, denominator) of every table entry -> normalised weights in pm[]
                 float mreg[ML_ITERS], lreg[ML_ITERS];
 #pragma unroll
@@ -1044,6 +1074,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     if (it < nent) {
                         const int o = sm.offs[it];
                         if (o >= 0) {
+                            // no grid barrier after P2: every record carries the epoch of its layer,
+                            // stamped after its contents; poll it (bounded) before reading the record
+                            if (!p.part_any_epoch) {
+                                const unsigned* ew = reinterpret_cast<const unsigned*>(pbase + o + D + 2);
+                                if (ld_acquire_u32(ew) != pep)
+                                    wait_bounded([&] { return ld_acquire_u32(ew) == pep; }, ab, ST_TIMEOUT_GRID);
+                            }
                             mreg[k] = ld_cg_f32(pbase + o + D);
                             lreg[k] = ld_cg_f32(pbase + o + D + 1);
                         }
@@ -1145,7 +1182,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.warp = warp;
         co.lane = lane;
         unsigned epoch = 0;
-        uint32_t xparity = 0, hparity = 0;
+        uint32_t xparity = 0, hparity = 0, mparity = 0;
+        const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
         const int pos_off = p.rope_stride * seq;
         const float* cosr = p.cos + pos_off;
         const float* sinr = p.sin + pos_off;
@@ -1224,14 +1262,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         },
                         [&]() {});
                 }
-                if (tid == 0) trace_mark(p, cta, l, TR_P1_DONE);
+                // count this CTA past P1: its share of the MLP intermediate is written
+                consumer_sync(NCTHR);
+                if (tid == 0) {
+                    __threadfence();
+                    atomicAdd(p.sync + 3, 1u);
+                    trace_mark(p, cta, l, TR_P1_DONE);
+                }
                 need_barrier = true;
             }
 
             // ------------------------------------------------------------ P2
             if (p.phase_mask & PH_P2) {
                 // no grid barrier here: q/k/v words carry their epoch and are polled where they are used
-                const QkvView qkv{p.qkv_ll, ll_base + static_cast<unsigned>(l) + 1u, p.qkv_any_epoch != 0, &ab};
+                const unsigned pep = ll_base + static_cast<unsigned>(l) + 1u;  // epoch of this layer's records
+                const QkvView qkv{p.qkv_ll, pep, p.qkv_any_epoch != 0, &ab};
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR1);
                 // Empty cache (seq == 0): there are no items, so the head's owner CTA turns the
                 // new token into the head's only partial.  Otherwise the CTA that streams the
@@ -1261,6 +1306,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             p.attn_new[h * PREC + D] = s;
                             p.attn_new[h * PREC + D + 1] = 1.0f;
                         }
+                        __syncwarp();
+                        if (lane == 0) publish_record(p.attn_new + h * PREC + D + 2, pep);
                     }
                 }
                 // cached rows: items [t2a, t2b), head-major
@@ -1304,6 +1351,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                     consumer_sync(NCTHR);
+                    if (tid == 0) publish_record(dst + D + 2, pep);
                 };
 
                 for (int t = t2a; t < t2b; ++t) {
@@ -1431,7 +1479,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
             // ------------------------------------------------------------ P3
             if (p.phase_mask & PH_P3) {
-                if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+                // No grid barrier: the helper warps poll the attention partials record by record, and
+                // one of their threads has watched the count of CTAs past P1 for the MLP intermediate.
+                if (mid_wait) {
+                    mbar_wait(smem_u32(sm.mid_ready), mparity, ab, ST_TIMEOUT_GRID);
+                    mparity ^= 1u;
+                }
                 if (tid == 0) trace_mark(p, cta, l, TR_BAR2);
                 // ---- this CTA's K slice of [mid ; attn] as fp32 in xbuf, chunk-major, MLP chunks
                 // first.  The helper warps merge the attention partials into the chunks behind
@@ -1661,6 +1714,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (old == static_cast<unsigned>(G) - 1u) {
                     p.sync[0] = 0u;
                     p.sync[1] = 0u;
+                    p.sync[3] = 0u;
                     *p.launch_count = *p.launch_count + 1u;
                     if (p.seq_inc) *p.seq_inc = seq + 1;
                     if (p.tp_size > 1) *p.tp_launch_count = *p.tp_launch_count + 1u;
