@@ -302,6 +302,8 @@ int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* 
     int xb = 2 * d.hidden;  // both LayerNorm outputs of a layer side by side
     if (ceil_div(kc3, cs) * KCHUNK > xb) xb = ceil_div(kc3, cs) * KCHUNK;
     if (16 * d.head_dim + 32 > xb) xb = 16 * d.head_dim + 32;
+    // pre-staged queries of up to MAXL heads (q, new k, new v) behind the LayerNorm outputs
+    if (qpre_offset(d.hidden, d.head_dim) + MAXL * 3 * d.head_dim > xb) xb = qpre_offset(d.hidden, d.head_dim) + MAXL * 3 * d.head_dim;
     xb = (xb + 3) / 4 * 4;
     const long fixed = static_cast<long>(smem_bytes_for(0, xb));
     int ns = static_cast<int>((ds.smem_optin - fixed) / STAGE_BYTES);

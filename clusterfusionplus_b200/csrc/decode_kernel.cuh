@@ -253,12 +253,14 @@ struct Smem {
     uint64_t* h_go;        // consumers -> helpers: the barrier before P3 has been passed
     uint64_t* attn_ready;  // helpers -> consumers: merged attention chunks are in xbuf
     uint64_t* mid_ready;   // helper thread -> consumers: every CTA is past P1, the MLP intermediate is complete
+    uint64_t* h_layer;     // consumers -> helpers: a new layer has begun, xbuf's spare region is free
+    uint64_t* q_ready;     // helpers -> consumers: this layer's rotated queries (and new k, v) are in xbuf
     int* abort_flag;
 };
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 4) * 8 + 16;
+           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 6) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -279,9 +281,15 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.h_go = s.xbar + 1;
     s.attn_ready = s.xbar + 2;
     s.mid_ready = s.xbar + 3;
-    s.abort_flag = reinterpret_cast<int*>(s.xbar + 4);
+    s.h_layer = s.xbar + 4;
+    s.q_ready = s.xbar + 5;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 6);
     return s;
 }
+
+// Where the helper warps leave the pre-staged queries in xbuf: behind both LayerNorm outputs
+// (live through P1) and behind P2's merge buffer; [MAXL][3][D] floats.
+__host__ __device__ __forceinline__ int qpre_offset(int H, int D) { return max(2 * H, 16 * D + 32); }
 
 // ---------------------------------------------------------------- math helpers
 __device__ __forceinline__ float gelu_tanh_f(float x) {
@@ -876,6 +884,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         mbar_init(smem_u32(sm.h_go), 1);
         mbar_init(smem_u32(sm.attn_ready), NHWARP);
         mbar_init(smem_u32(sm.mid_ready), 1);
+        mbar_init(smem_u32(sm.h_layer), 1);
+        mbar_init(smem_u32(sm.q_ready), NHWARP);
         mbar_fence_init();
     }
     __syncthreads();
@@ -1028,12 +1038,85 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 mbar_arrive(smem_u32(sm.mid_ready));
             }
         };
-        if ((p.phase_mask & PH_P3) && nattn == 0) {
-            for (int l = 0; l < p.n_layers; ++l) watch_mid(l);
-        }
-        if ((p.phase_mask & PH_P3) && nattn > 0) {
+        const bool do_merge = (p.phase_mask & PH_P3) && nattn > 0;
+        // P2 set-up done ahead of the consumers: the rotated, scaled query of every head this CTA
+        // streams, and the new token's key and value where it streams the head's last chunk
+        // (appended to the cache here), as fp32 in the spare region of xbuf.  The q/k/v words are
+        // polled while the consumers are still in P1.
+        const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
+        const unsigned hl_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
+        uint32_t lpar = 0;
+        auto stage_q = [&](int l) {
+            mbar_wait(smem_u32(sm.h_layer), lpar, ab, ST_TIMEOUT_GRID);
+            lpar ^= 1u;
+            const LayerDesc* L = p.layers + l;
+            const QkvView qkv{p.qkv_ll, hl_base + static_cast<unsigned>(l) + 1u, p.qkv_any_epoch != 0, &ab};
+            const int pos_off = p.rope_stride * seq;
+            const float* cosr = p.cos + pos_off;
+            const float* sinr = p.sin + pos_off;
+            const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
+            float* qpre = sm.xbuf + qpre_offset(H, D);
+            const int h_first = t2a / nch, h_last = (t2b - 1) / nch;
+            for (int h = h_first; h <= h_last; ++h) {
+                const bool has_last = (h + 1) * nch - 1 < t2b;
+                const int qi = h * 3 * D;
+                float* dst = qpre + (h - h_first) * 3 * D;
+                // all of this thread's words (and their rotation partners) in flight at once; the
+                // epochs are checked together and the batch is re-read (bounded) until all match
+                const int ne = has_last ? 3 * D : D;
+                const int half_r = R >> 1;
+                constexpr int KQ = (3 * D + NHTHR - 1) / NHTHR;
+                uint2 w[KQ], wp[KQ];
+                auto fetch = [&]() {
+                    bool ok = true;
+#pragma unroll
+                    for (int k = 0; k < KQ; ++k) {
+                        const int e = ht + k * NHTHR;
+                        if (e < ne) {
+                            const int part = e / D, d = e - part * D;
+                            w[k] = ld_ll(qkv.base + qi + e);
+                            ok = ok && (qkv.any || w[k].y == qkv.epoch);
+                            if (part < 2 && d < R) {
+                                wp[k] = ld_ll(qkv.base + qi + e + (d < half_r ? half_r : -half_r));
+                                ok = ok && (qkv.any || wp[k].y == qkv.epoch);
+                            }
+                        }
+                    }
+                    return ok;
+                };
+                if (!fetch()) wait_bounded(fetch, ab, ST_TIMEOUT_PEER);
+#pragma unroll
+                for (int k = 0; k < KQ; ++k) {
+                    const int e = ht + k * NHTHR;
+                    if (e >= ne) continue;
+                    const int part = e / D, d = e - part * D;
+                    float val = __uint_as_float(w[k].x);
+                    if (part < 2 && d < R) {
+                        const float partner = __uint_as_float(wp[k].x);
+                        val = val * __ldg(cosr + d) + ((d < half_r) ? -partner : partner) * __ldg(sinr + d);
+                    }
+                    if (part == 0) {
+                        dst[d] = val * qscale;
+                    } else {
+                        const __half h16 = __float2half_rn(val);
+                        dst[part * D + d] = __half2float(h16);
+                        const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
+                        if (part == 1) {
+                            if (!(p.arch_flags & AF_NO_APPEND)) L->k_cache[off] = h16;
+                            if (p.k_new) p.k_new[h * D + d] = h16;
+                        } else {
+                            if (!(p.arch_flags & AF_NO_APPEND)) L->v_cache[off] = h16;
+                            if (p.v_new) p.v_new[h * D + d] = h16;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(sm.q_ready));
+        };
+        {
             // Which partial feeds which of my chunks depends only on (grid, seq): tabulate once.
-            for (int it = ht; it < nent; it += NHTHR) {
+            for (int it = ht; do_merge && it < nent; it += NHTHR) {
                 const int pair = it / pstr, j = it - pair * pstr;
                 const int i = pair / HPC, hh = pair - i * HPC;
                 const int q = me + i * CS;
@@ -1057,9 +1140,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
             constexpr int ML_ITERS = (WTS_SLOTS + NHTHR - 1) / NHTHR;
             uint32_t gpar = 0;
-            const unsigned hl_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
             for (int l = 0; l < p.n_layers; ++l) {
-                watch_mid(l);
+                if (do_q) stage_q(l);
+                if (p.phase_mask & PH_P3) watch_mid(l);
+                if (!do_merge) continue;
                 // the consumers have left P2 of this layer: xbuf's attention chunks are free
                 mbar_wait(smem_u32(sm.h_go), gpar, ab, ST_TIMEOUT_GRID);
                 gpar ^= 1u;
@@ -1182,7 +1266,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.warp = warp;
         co.lane = lane;
         unsigned epoch = 0;
-        uint32_t xparity = 0, hparity = 0, mparity = 0;
+        uint32_t xparity = 0, hparity = 0, mparity = 0, qparity = 0;
+        const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
         const int pos_off = p.rope_stride * seq;
         const float* cosr = p.cos + pos_off;
@@ -1211,6 +1296,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (y) y[row] = hv;
                 else st_ll(yll + row, static_cast<unsigned>(__half_as_ushort(hv)), yep);
             };
+
+            // every consumer thread is past the previous layer's last read of xbuf
+            if (do_q && tid == 0) mbar_arrive(smem_u32(sm.h_layer));
 
             // ------------------------------------------------------------ P1
             if (p.phase_mask & PH_P1) {
@@ -1318,6 +1406,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 int cur_h = -1;
                 float qreg[8], acc[8], m_run = -INFINITY, l_run = 0.f;
                 const int h_first = (t2b > t2a) ? t2a / nch : 0;
+                const float* qpre = sm.xbuf + qpre_offset(H, D);
+                const float* hq = qpre;
+                if (do_q) {
+                    mbar_wait(smem_u32(sm.q_ready), qparity, ab, ST_TIMEOUT_GRID);
+                    qparity ^= 1u;
+                }
 
                 auto flush = [&](int h) {
                     const int slot = warp * 2 + hw;
@@ -1359,33 +1453,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     if (h != cur_h) {
                         if (cur_h >= 0) flush(cur_h);
                         cur_h = h;
-                        // q for every CTA on this head; k, v (fp16-rounded, appended to the
-                        // cache) only where the head's last chunk is streamed
-                        const bool has_last = (h + 1) * nch - 1 < t2b;
-                        const int qi = h * 3 * D;
-                        for (int e = tid; e < (has_last ? 3 * D : D); e += NCTHR) {
-                            const int part = e / D, d = e - part * D;
-                            if (part == 0) {
-                                sm.q_s[d] = rope_elem(qkv, qi, d, R, cosr, sinr) * qscale;
-                            } else {
-                                const float val = (part == 1) ? rope_elem(qkv, qi + D, d, R, cosr, sinr)
-                                                              : qkv.get(qi + 2 * D + d);
-                                const __half h16 = __float2half_rn(val);
-                                sm.kv_s[(part - 1) * D + d] = __half2float(h16);
-                                const size_t off = static_cast<size_t>(seq) * KVW + h * D + d;
-                                if (part == 1) {
-                                    if (!(p.arch_flags & AF_NO_APPEND)) L->k_cache[off] = h16;
-                                    if (p.k_new) p.k_new[h * D + d] = h16;
-                                } else {
-                                    if (!(p.arch_flags & AF_NO_APPEND)) L->v_cache[off] = h16;
-                                    if (p.v_new) p.v_new[h * D + d] = h16;
-                                }
-                            }
-                        }
-                        consumer_sync(NCTHR);
+                        // the helper warps staged q (and the new k, v where this CTA streams the
+                        // head's last chunk) while P1 was still running
+                        hq = qpre + (h - h_first) * 3 * D;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
-                            qreg[k] = dim_ok ? sm.q_s[l16 * 8 + k] : 0.f;
+                            qreg[k] = dim_ok ? hq[l16 * 8 + k] : 0.f;
                             acc[k] = 0.f;
                         }
                         m_run = -INFINITY;
@@ -1458,7 +1531,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         float sn = 0.f;
                         if (dim_ok) {
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) sn = fmaf(qreg[k], sm.kv_s[l16 * 8 + k], sn);
+                            for (int k = 0; k < 8; ++k) sn = fmaf(qreg[k], hq[D + l16 * 8 + k], sn);
                         }
 #pragma unroll
                         for (int o = 8; o > 0; o >>= 1) sn += __shfl_xor_sync(0x0000ffffu, sn, o);
@@ -1467,7 +1540,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         l_run = fmaf(l_run, sc, pn);
                         if (dim_ok) {
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) acc[k] = fmaf(acc[k], sc, pn * sm.kv_s[D + l16 * 8 + k]);
+                            for (int k = 0; k < 8; ++k) acc[k] = fmaf(acc[k], sc, pn * hq[2 * D + l16 * 8 + k]);
                         }
                         m_run = mx;
                     }
