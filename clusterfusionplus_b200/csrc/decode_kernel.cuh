@@ -1671,10 +1671,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const TailDesc* Tl = p.tail;
             const __half* x = (p.n_layers > 0) ? p.out : x_first;
             if (need_barrier) grid_barrier(p.sync, epoch, G, tid, ab);
+            if (tid == 0) trace_mark(p, cta, p.n_layers, TR_START);
             float best = -INFINITY;
             int best_i = 0x7fffffff;
             if (g4b > g4a) {
                 layer_norm_to_smem(x, Tl->fln_w, Tl->fln_b, H, sm.xbuf, sm.red, tid, false);
+                if (tid == 0) trace_mark(p, cta, p.n_layers, TR_LN_DONE);
                 const int row0 = g4a * GRAN, V = Tl->vocab;
                 float* lg = p.logits;
                 co.rows_phase(g4b - g4a, KC1, sm.xbuf, [&](int g, int r, float v) {
@@ -1688,6 +1690,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                 });
             }
+            if (tid == 0) trace_mark(p, cta, p.n_layers, TR_P1_DONE);
             // arg-max: warp, then CTA, then (after a grid barrier) CTA 0
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -1716,6 +1719,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 p.amax_idx[cta] = best_i;
             }
             grid_barrier(p.sync, epoch, G, tid, ab);
+            if (tid == 0) trace_mark(p, cta, p.n_layers, TR_BAR1);
             if (cta == 0 && warp == 0) {
                 float b = -INFINITY;
                 int bi = 0x7fffffff;
