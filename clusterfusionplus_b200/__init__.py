@@ -16,5 +16,6 @@ from .api import (  # noqa: F401
     pythia_6b9_create_graph_context, pythia_6b9_decoder_layer, pythia_6b9_decoder_layer_split,
     pythia_6b9_destroy_graph_context, pythia_6b9_graph_decode_step, pythia_6b9_graph_set_device_state,
 )
+from .checkpoint import convert_state_dict, describe_config, load_decoder  # noqa: F401
 from .decoder import PythiaDecoder, rope_table  # noqa: F401
 from .tp import TPDecoder, shard_cache, shard_dims, shard_head_weights, shard_layer_weights  # noqa: F401

@@ -41,7 +41,10 @@ class CfStepArgs(C.Structure):
 
 class CfDecoderConfig(C.Structure):
     _fields_ = [("dims", CfDims), ("n_layers", C.c_int), ("max_seq_len", C.c_int64), ("tp_size", C.c_int),
-                ("tp_rank", C.c_int), ("cos_table", C.c_void_p), ("sin_table", C.c_void_p)]
+                ("tp_rank", C.c_int), ("cos_table", C.c_void_p), ("sin_table", C.c_void_p), ("flags", C.c_int)]
+
+
+CF_DECODER_GELU_ERF = 1
 
 
 class CfHeadWeights(C.Structure):

@@ -612,6 +612,7 @@ void decoder_params(Decoder& dc, Params& p) {
     p.sin = dc.cfg.sin_table;
     p.rope_stride = dc.cfg.dims.rotary;
     p.seq_ptr = dc.seq_d;
+    if (dc.cfg.flags & CF_DECODER_GELU_ERF) p.arch_flags |= AF_GELU_ERF;
 }
 
 // ---------------------------------------------------------------------------

@@ -66,6 +66,7 @@ enum : int {
     AF_RMS_ADD = 1,     // norm = RMSNorm(x + residual) with weight only; the sum is also an output
     AF_QKV_PLANAR = 2,  // QKV weight rows are [Q of all heads; K of all heads; V of all heads]
     AF_NO_APPEND = 4,   // the caches hold exactly seq_len rows and are not written
+    AF_GELU_ERF = 8,    // MLP activation is the exact GELU x * Phi(x) instead of the tanh form
 };
 enum : int {
     F3_USE_O = 1,       // include W_o chunks (attention output) in P3
@@ -292,6 +293,7 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
 __host__ __device__ __forceinline__ int qpre_offset(int H, int D) { return max(2 * H, 16 * D + 32); }
 
 // ---------------------------------------------------------------- math helpers
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f)); }
 __device__ __forceinline__ float gelu_tanh_f(float x) {
     const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     return 0.5f * x * (1.0f + tanhf(u));
@@ -1344,7 +1346,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         },
                         [&](int g, int r, float v) {
                             const int row = rowu0 + g * GRAN + r;
-                            const float a = gelu_tanh_f(v + __half2float(__ldg(bu + row)));
+                            const float pre = v + __half2float(__ldg(bu + row));
+                            const float a = (p.arch_flags & AF_GELU_ERF) ? gelu_erf_f(pre) : gelu_tanh_f(pre);
                             dm[row] = a;
                             if (dm16) dm16[row] = __float2half_rn(a);
                         },

@@ -10,9 +10,10 @@ import ctypes as C
 from typing import Dict, List, Optional, Sequence
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
-from ._lib import CfDecoderConfig, CfDims, CfHeadWeights, CfLayerWeights, check, lib
+from ._lib import CF_DECODER_GELU_ERF, CfDecoderConfig, CfDims, CfHeadWeights, CfLayerWeights, check, lib
 from .api import _req, _wrap
 
 _LAYER_KEYS = {
@@ -53,17 +54,20 @@ class PythiaDecoder:
     """
 
     def __init__(self, dims: CfDims, layers: Sequence[Dict[str, torch.Tensor]], head: Dict[str, torch.Tensor],
-                 caches: Sequence, max_seq: int, use_graph: bool = True):
+                 caches: Sequence, max_seq: int, use_graph: bool = True, flags: int = 0,
+                 rope_base: float = 10000.0):
         self.dims, self.layers, self.head, self.caches = dims, list(layers), head, list(caches)
         self.max_seq = int(max_seq)
+        self.flags = int(flags)
         self.device = head["embed_in"].device
-        self.cos, self.sin = rope_table(self.max_seq, dims.rotary, self.device)
+        self.cos, self.sin = rope_table(self.max_seq, dims.rotary, self.device, rope_base)
         cfg = CfDecoderConfig()
         cfg.dims = dims
         cfg.n_layers = len(self.layers)
         cfg.max_seq_len = self.max_seq
         cfg.tp_size, cfg.tp_rank = 1, 0
         cfg.cos_table, cfg.sin_table = self.cos.data_ptr(), self.sin.data_ptr()
+        cfg.flags = self.flags
         h = C.c_int64(0)
         check(lib.cf_decoder_create(C.byref(cfg), C.byref(h)))
         self.handle = h.value
@@ -131,6 +135,58 @@ class PythiaDecoder:
         """Greedy rollout; returns the n_tokens generated ids (one host read per token,
         like the reference loop's .item())."""
         self.reset(seq_len, first_token)
+        out = []
+        for _ in range(n_tokens):
+            self.step()
+            out.append(int(self.token.item()))
+        return out
+
+    @torch.no_grad()
+    def prefill(self, tokens: Sequence[int]) -> None:
+        """Ingest a prompt.  Rows [0, n-1) of every cache are computed for all prompt positions
+        at once with library kernels (cuBLAS GEMMs, torch's fused causal attention) -- the
+        reference leaves prefill to the HuggingFace model in the same way
+        (tests/benchmark_full.py:195-199).  The decoder is then positioned on the last prompt
+        token, so the next step() consumes it through the fused kernel and yields the first
+        generated token."""
+        ids = torch.as_tensor(list(tokens), dtype=torch.long, device=self.device)
+        n = int(ids.numel())
+        if n < 1 or n > self.max_seq - 1:
+            raise RuntimeError(f"prompt of {n} tokens does not fit {self.max_seq} cache rows")
+        m = n - 1
+        if m > 0:
+            d = self.dims
+            H, NH, D, R = d.hidden, d.heads, d.head_dim, d.rotary
+            approx = "none" if (self.flags & CF_DECODER_GELU_ERF) else "tanh"
+            cos, sin = self.cos[:m, None, :], self.sin[:m, None, :]  # [m, 1, R] fp32
+
+            def rope(t):  # [m, NH, D] fp16 -> rotate-half on the first R dims, fp32 math
+                r = t[..., :R].float()
+                half = torch.cat([-r[..., R // 2:], r[..., : R // 2]], dim=-1)
+                return torch.cat([(r * cos + half * sin).to(t.dtype), t[..., R:]], dim=-1)
+
+            def norm(x, w, b):
+                return F.layer_norm(x.float(), (H,), w.float(), b.float(), 1e-5).to(x.dtype)
+
+            x = self.head["embed_in"][ids[:m]]
+            for w, (kc, vc) in zip(self.layers, self.caches):
+                qkv = F.linear(norm(x, w["ln_weight"].reshape(-1), w["ln_bias"].reshape(-1)), w["qkv_weight"],
+                               w["qkv_bias"]).view(m, NH, 3, D)
+                q, k, v = rope(qkv[:, :, 0]), rope(qkv[:, :, 1]), qkv[:, :, 2]
+                kc[:m] = k.reshape(m, NH * D)
+                vc[:m] = v.reshape(m, NH * D)
+                attn = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
+                                                      v.transpose(0, 1)[None], is_causal=True)
+                attn = attn[0].transpose(0, 1).reshape(m, NH * D)
+                mid = F.gelu(F.linear(norm(x, w["post_ln_weight"].reshape(-1), w["post_ln_bias"].reshape(-1)),
+                                      w["mlp_up_weight"], w["mlp_up_bias"]).float(), approximate=approx).to(x.dtype)
+                x = (x.float() + F.linear(attn, w["o_weight"], w["o_bias"]).float()
+                     + F.linear(mid, w["mlp_down_weight"], w["mlp_down_bias"]).float()).to(x.dtype)
+        self.reset(m, int(ids[-1].item()))
+
+    def generate_from_prompt(self, tokens: Sequence[int], n_tokens: int) -> List[int]:
+        """prefill(tokens), then n_tokens greedy steps; returns the generated ids."""
+        self.prefill(tokens)
         out = []
         for _ in range(n_tokens):
             self.step()

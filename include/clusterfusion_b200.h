@@ -221,7 +221,13 @@ typedef struct CfDecoderConfig {
     int tp_rank;
     const float* cos_table;  /* [max_seq_len, rotary] fp32 */
     const float* sin_table;
+    int flags;               /* CF_DECODER_* */
 } CfDecoderConfig;
+
+/* MLP activation is the exact (erf) GELU, as in the published Pythia checkpoints
+ * (hidden_act "gelu"), instead of the tanh form the reference kernels hard-code
+ * (include/5090/pythia_6b9/kernel.cuh:39-54). */
+#define CF_DECODER_GELU_ERF 1
 
 typedef struct CfHeadWeights {
     const void* embed_in;         /* [vocab_total, hidden] */

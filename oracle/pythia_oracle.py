@@ -169,10 +169,14 @@ def gelu_tanh(x):
     return 0.5 * x * (1.0 + torch.tanh(GELU_C * (x + GELU_K * x * x * x)))
 
 
+def gelu_erf(x):
+    return 0.5 * x * (1.0 + torch.erf(x * 0.7071067811865476))
+
+
 def layer_decode_fp32(shape: Shape, x: torch.Tensor, w: Dict[str, torch.Tensor],
                       k_cache: torch.Tensor, v_cache: torch.Tensor,
                       cos: torch.Tensor, sin: torch.Tensor, seq_len: int,
-                      intermediates: Optional[dict] = None, partial: bool = False):
+                      intermediates: Optional[dict] = None, partial: bool = False, act: str = "tanh"):
     """One decode step of one layer in fp32.
 
     x [1,H]; caches [rows, NH*D] of which rows [0, seq_len) are history (not
@@ -183,6 +187,8 @@ def layer_decode_fp32(shape: Shape, x: torch.Tensor, w: Dict[str, torch.Tensor],
     narrower MLP, full hidden width).  With partial=True the result is the shard's
     contribution attn @ Wo^T + mid @ Wdown^T only: no residual, no dense / down bias
     (those are added once, after the partials of all shards are summed).
+    act = "tanh" is the reference kernels' GELU (kernel.cuh:39-54), "erf" the exact
+    form of the published checkpoints (HF hidden_act "gelu").
     """
     H, NH, D, R = shape.hidden, shape.heads, shape.head_dim, shape.rotary
     f = lambda t: t.detach().to("cpu", torch.float32)
@@ -208,7 +214,8 @@ def layer_decode_fp32(shape: Shape, x: torch.Tensor, w: Dict[str, torch.Tensor],
     attn = torch.einsum("hs,hsd->hd", p, v_all).reshape(1, NH * D)
 
     attn_out = attn @ W["o_weight"].t() + W["o_bias"]
-    mid = gelu_tanh(y2 @ W["mlp_up_weight"].t() + W["mlp_up_bias"])
+    pre = y2 @ W["mlp_up_weight"].t() + W["mlp_up_bias"]
+    mid = gelu_erf(pre) if act == "erf" else gelu_tanh(pre)
     mlp_out = mid @ W["mlp_down_weight"].t() + W["mlp_down_bias"]
     out = x + attn_out + mlp_out
     if partial:
@@ -240,13 +247,14 @@ class OracleModel:
     the layer output), so a rollout compares like with like.
     """
 
-    def __init__(self, shape: Shape, layers, head, max_seq: int, round_io: bool = True):
-        self.shape, self.head, self.max_seq, self.round_io = shape, head, max_seq, round_io
+    def __init__(self, shape: Shape, layers, head, max_seq: int, round_io: bool = True, act: str = "tanh",
+                 rope_base: float = 10000.0):
+        self.shape, self.head, self.max_seq, self.round_io, self.act = shape, head, max_seq, round_io, act
         self.layers = [{k: v.detach().to("cpu", torch.float32) for k, v in w.items()} for w in layers]
         W = shape.heads * shape.head_dim
         self.k = [torch.zeros(max_seq, W) for _ in layers]
         self.v = [torch.zeros(max_seq, W) for _ in layers]
-        self.cos, self.sin = rope_table(max_seq, shape.rotary)
+        self.cos, self.sin = rope_table(max_seq, shape.rotary, base=rope_base)
         self.seq_len = 0
 
     def load_cache(self, layer: int, k: torch.Tensor, v: torch.Tensor, seq_len: int):
@@ -259,7 +267,7 @@ class OracleModel:
         x = self.head["embed_in"][token].detach().to("cpu", torch.float32).reshape(1, -1)
         for i, w in enumerate(self.layers):
             x, kn, vn = layer_decode_fp32(self.shape, x, w, self.k[i], self.v[i],
-                                          self.cos[s], self.sin[s], s)
+                                          self.cos[s], self.sin[s], s, act=self.act)
             if self.round_io:
                 x, kn, vn = round_fp16(x), round_fp16(kn), round_fp16(vn)
             self.k[i][s] = kn.reshape(-1)
