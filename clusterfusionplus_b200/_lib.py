@@ -45,6 +45,7 @@ class CfDecoderConfig(C.Structure):
 
 
 CF_DECODER_GELU_ERF = 1
+CF_ACT_NONE, CF_ACT_GELU_TANH, CF_ACT_GELU_ERF = 0, 1, 2
 
 
 class CfHeadWeights(C.Structure):
@@ -88,6 +89,8 @@ SIGNATURES = {
     "cf_decoder_tail": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_select_token": (C.c_int, [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_decoder_destroy": (C.c_int, [C.c_int64]),
+    "cf_prefill_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                    C.c_int64, C.c_int, C.c_void_p]),
 }
 
 

@@ -23,6 +23,7 @@
 
 #include "../../include/clusterfusion_b200.h"
 #include "decode_kernel.cuh"
+#include "prefill_gemm.h"
 
 using namespace cfb;
 
@@ -1411,6 +1412,23 @@ int cf_decoder_destroy(int64_t handle) {
     cudaFree(dc->token_d);
     cudaFree(dc->ws.base);
     delete dc;
+    return CF_OK;
+}
+
+int cf_prefill_linear(const void* x, const void* weight, const void* bias, const void* residual, void* out,
+                      int64_t m, int64_t n, int64_t k, int act, void* stream) {
+    if (!x || !weight || !out) return fail(CF_ERR_INVALID, "null argument");
+    if (m <= 0 || n <= 0 || k <= 0 || m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff)
+        return fail(CF_ERR_INVALID, "bad GEMM extent %lld x %lld x %lld", (long long)m, (long long)n, (long long)k);
+    if ((n % 8) || (k % 8)) return fail(CF_ERR_UNSUPPORTED, "n (%lld) and k (%lld) must be multiples of 8", (long long)n, (long long)k);
+    if (act != CF_ACT_NONE && act != CF_ACT_GELU_TANH && act != CF_ACT_GELU_ERF) return fail(CF_ERR_INVALID, "activation %d", act);
+    if (residual && act != CF_ACT_NONE) return fail(CF_ERR_INVALID, "a residual goes with CF_ACT_NONE only");
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    const char* msg = prefill_linear(x, weight, bias, residual, out, static_cast<int>(m), static_cast<int>(n),
+                                     static_cast<int>(k), act, static_cast<cudaStream_t>(stream));
+    if (msg) return fail(CF_ERR_CUDA, "prefill GEMM: %s", msg);
     return CF_OK;
 }
 

@@ -1,0 +1,110 @@
+// Prompt ingestion (prefill) linear layers on the 5th-generation tensor cores.
+//
+// out[m, n] = act(x[m, k] . W[n, k]^T + bias[n] + residual[m, n]), fp16 in and out, fp32
+// accumulation in tensor memory.  The kernel is assembled from CUTLASS's sm_100 building
+// blocks (TMA loads of both operands into shared memory, tcgen05.mma issued by one thread,
+// accumulators in TMEM, epilogue reading them back with tcgen05.ld), with bias, GELU and the
+// residual add fused into the epilogue so that no intermediate goes through HBM twice.
+//
+// Two tilings: a pair of SMs on one 256x128 output tile (tcgen05.mma cta_group::2, cluster 2x1,
+// each CTA of the pair loading its own rows of the activations and its own half of the weight
+// tile) when there are more than 128 rows, else one CTA per 128x128 tile.  No operand is shared
+// between pairs inside a cluster, so every TMA load is a plain one, never a multicast.
+//
+// The decode path never comes here: at one token per step the layers are memory-bound vector
+// products (decode_kernel.cuh).  This file serves the whole-prompt pass, where every weight is
+// reused across all prompt positions and the work is a real GEMM.
+#include <cuda_runtime.h>
+
+#include "cutlass/cutlass.h"
+#include "cute/tensor.hpp"
+#include "cutlass/numeric_types.h"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/epilogue/fusion/operations.hpp"
+#include "cutlass/epilogue/thread/activation.h"
+#include "cutlass/util/packed_stride.hpp"
+
+#include "prefill_gemm.h"
+
+namespace cfb {
+namespace {
+
+using namespace cute;
+
+template <template <class> class Act, class TileShape_, class ClusterShape_>
+struct LinearGemm {
+    using Element = cutlass::half_t;
+    using LayoutA = cutlass::layout::RowMajor;     // activations [m, k]
+    using LayoutB = cutlass::layout::ColumnMajor;  // weight [n, k] row-major == [k, n] column-major
+    using LayoutC = cutlass::layout::RowMajor;     // residual / output [m, n]
+    static constexpr int Align = 8;                // 16-byte rows: what TMA needs
+    using TileShape = TileShape_;
+    using ClusterShape = ClusterShape_;
+    using Fusion = cutlass::epilogue::fusion::LinCombPerColBiasEltAct<Act, Element, float, Element, Element, float>;
+    using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, TileShape, ClusterShape,
+        cutlass::epilogue::collective::EpilogueTileAuto, float, float, Element, LayoutC, Align, Element, LayoutC, Align,
+        cutlass::epilogue::collective::EpilogueScheduleAuto, Fusion>::CollectiveOp;
+    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Element, LayoutA, Align, Element, LayoutB, Align, float,
+        TileShape, ClusterShape,
+        cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+        cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+
+    static const char* run(const void* x, const void* w, const void* bias, const void* residual, void* out, int m,
+                           int n, int k, cudaStream_t st) {
+        using StrideA = typename Kernel::StrideA;
+        using StrideB = typename Kernel::StrideB;
+        using StrideC = typename Kernel::StrideC;
+        using StrideD = typename Kernel::StrideD;
+        const StrideA sa = cutlass::make_cute_packed_stride(StrideA{}, make_shape(m, k, 1));
+        const StrideB sb = cutlass::make_cute_packed_stride(StrideB{}, make_shape(n, k, 1));
+        const StrideC sc = cutlass::make_cute_packed_stride(StrideC{}, make_shape(m, n, 1));
+        const StrideD sd = cutlass::make_cute_packed_stride(StrideD{}, make_shape(m, n, 1));
+        typename Gemm::Arguments args{
+            cutlass::gemm::GemmUniversalMode::kGemm,
+            {m, n, k, 1},
+            {static_cast<const Element*>(x), sa, static_cast<const Element*>(w), sb},
+            {{}, static_cast<const Element*>(residual), sc, static_cast<Element*>(out), sd}};
+        args.epilogue.thread.alpha = 1.0f;
+        args.epilogue.thread.beta = residual ? 1.0f : 0.0f;
+        args.epilogue.thread.bias_ptr = static_cast<const Element*>(bias);
+        Gemm gemm;
+        if (gemm.can_implement(args) != cutlass::Status::kSuccess) return "shape or alignment not supported by the GEMM";
+        if (Gemm::get_workspace_size(args) != 0) return "unexpected GEMM workspace";
+        if (gemm.initialize(args, nullptr, st) != cutlass::Status::kSuccess) return "GEMM initialisation failed";
+        if (gemm.run(st) != cutlass::Status::kSuccess) return "GEMM launch failed";
+        return nullptr;
+    }
+};
+
+template <template <class> class Act>
+const char* dispatch(const void* x, const void* w, const void* bias, const void* residual, void* out, int m, int n, int k,
+                     cudaStream_t st) {
+    if (m > 128)
+        return LinearGemm<Act, Shape<_256, _128, _64>, Shape<_2, _1, _1>>::run(x, w, bias, residual, out, m, n, k, st);
+    return LinearGemm<Act, Shape<_128, _128, _64>, Shape<_1, _1, _1>>::run(x, w, bias, residual, out, m, n, k, st);
+}
+
+}  // namespace
+
+const char* prefill_linear(const void* x, const void* w, const void* bias, const void* residual, void* out, int m, int n,
+                           int k, int act, cudaStream_t st) {
+    switch (act) {
+        case PREFILL_ACT_NONE:
+            return dispatch<cutlass::epilogue::thread::Identity>(x, w, bias, residual, out, m, n, k, st);
+        case PREFILL_ACT_GELU_TANH:
+            return dispatch<cutlass::epilogue::thread::GELU_taylor>(x, w, bias, residual, out, m, n, k, st);
+        case PREFILL_ACT_GELU_ERF:
+            return dispatch<cutlass::epilogue::thread::GELU>(x, w, bias, residual, out, m, n, k, st);
+        default:
+            return "unknown activation";
+    }
+}
+
+}  // namespace cfb

@@ -13,7 +13,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
-from ._lib import CF_DECODER_GELU_ERF, CfDecoderConfig, CfDims, CfHeadWeights, CfLayerWeights, check, lib
+from ._lib import CF_ACT_GELU_ERF, CF_ACT_GELU_TANH, CF_ACT_NONE, CF_DECODER_GELU_ERF, CfDecoderConfig, CfDims, CfHeadWeights, CfLayerWeights, check, lib
 from .api import _req, _wrap
 
 _LAYER_KEYS = {
@@ -43,6 +43,20 @@ def layer_weights_struct(d: CfDims, w: Dict[str, torch.Tensor]) -> CfLayerWeight
     for field, key in _LAYER_KEYS.items():
         setattr(s, field, _req(w[key], key, sizes[field]))
     return s
+
+
+def prefill_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None, act: int = CF_ACT_NONE) -> torch.Tensor:
+    """act(x @ weight.T + bias + residual) for fp16 x [m, k], weight [n, k] on the tensor cores
+    (cf_prefill_linear: TMA-fed tcgen05 GEMM with the bias, GELU and residual fused in)."""
+    m, k = x.shape
+    n = weight.shape[0]
+    out = torch.empty(m, n, device=x.device, dtype=torch.float16)
+    check(lib.cf_prefill_linear(_req(x, "x", m * k), _req(weight, "weight", n * k),
+                                None if bias is None else _req(bias, "bias", n),
+                                None if residual is None else _req(residual, "residual", m * n),
+                                out.data_ptr(), m, n, k, act, torch.cuda.current_stream().cuda_stream))
+    return out
 
 
 class PythiaDecoder:
@@ -144,11 +158,12 @@ class PythiaDecoder:
     @torch.no_grad()
     def prefill(self, tokens: Sequence[int]) -> None:
         """Ingest a prompt.  Rows [0, n-1) of every cache are computed for all prompt positions
-        at once with library kernels (cuBLAS GEMMs, torch's fused causal attention) -- the
-        reference leaves prefill to the HuggingFace model in the same way
-        (tests/benchmark_full.py:195-199).  The decoder is then positioned on the last prompt
-        token, so the next step() consumes it through the fused kernel and yields the first
-        generated token."""
+        at once: the four linear layers of a block run as tensor-core GEMMs with their bias,
+        GELU and residual fused (cf_prefill_linear); LayerNorm, RoPE and the causal attention
+        over the prompt are torch library kernels.  The reference has no prefill of its own and
+        leaves it to the HuggingFace model (tests/benchmark_full.py:195-199).  The decoder is
+        then positioned on the last prompt token, so the next step() consumes it through the
+        fused decode kernel and yields the first generated token."""
         ids = torch.as_tensor(list(tokens), dtype=torch.long, device=self.device)
         n = int(ids.numel())
         if n < 1 or n > self.max_seq - 1:
@@ -157,7 +172,7 @@ class PythiaDecoder:
         if m > 0:
             d = self.dims
             H, NH, D, R = d.hidden, d.heads, d.head_dim, d.rotary
-            approx = "none" if (self.flags & CF_DECODER_GELU_ERF) else "tanh"
+            gelu = CF_ACT_GELU_ERF if (self.flags & CF_DECODER_GELU_ERF) else CF_ACT_GELU_TANH
             cos, sin = self.cos[:m, None, :], self.sin[:m, None, :]  # [m, 1, R] fp32
 
             def rope(t):  # [m, NH, D] fp16 -> rotate-half on the first R dims, fp32 math
@@ -168,20 +183,21 @@ class PythiaDecoder:
             def norm(x, w, b):
                 return F.layer_norm(x.float(), (H,), w.float(), b.float(), 1e-5).to(x.dtype)
 
-            x = self.head["embed_in"][ids[:m]]
+            x = self.head["embed_in"][ids[:m]].contiguous()
             for w, (kc, vc) in zip(self.layers, self.caches):
-                qkv = F.linear(norm(x, w["ln_weight"].reshape(-1), w["ln_bias"].reshape(-1)), w["qkv_weight"],
-                               w["qkv_bias"]).view(m, NH, 3, D)
+                y1 = norm(x, w["ln_weight"].reshape(-1), w["ln_bias"].reshape(-1))
+                qkv = prefill_linear(y1, w["qkv_weight"], w["qkv_bias"]).view(m, NH, 3, D)
                 q, k, v = rope(qkv[:, :, 0]), rope(qkv[:, :, 1]), qkv[:, :, 2]
                 kc[:m] = k.reshape(m, NH * D)
                 vc[:m] = v.reshape(m, NH * D)
                 attn = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
                                                       v.transpose(0, 1)[None], is_causal=True)
-                attn = attn[0].transpose(0, 1).reshape(m, NH * D)
-                mid = F.gelu(F.linear(norm(x, w["post_ln_weight"].reshape(-1), w["post_ln_bias"].reshape(-1)),
-                                      w["mlp_up_weight"], w["mlp_up_bias"]).float(), approximate=approx).to(x.dtype)
-                x = (x.float() + F.linear(attn, w["o_weight"], w["o_bias"]).float()
-                     + F.linear(mid, w["mlp_down_weight"], w["mlp_down_bias"]).float()).to(x.dtype)
+                attn = attn[0].transpose(0, 1).reshape(m, NH * D).contiguous()
+                y2 = norm(x, w["post_ln_weight"].reshape(-1), w["post_ln_bias"].reshape(-1))
+                mid = prefill_linear(y2, w["mlp_up_weight"], w["mlp_up_bias"], act=gelu)
+                # parallel residual: x + attention branch, then + MLP branch, each add in a GEMM epilogue
+                h = prefill_linear(attn, w["o_weight"], w["o_bias"], residual=x)
+                x = prefill_linear(mid, w["mlp_down_weight"], w["mlp_down_bias"], residual=h)
         self.reset(m, int(ids[-1].item()))
 
     def generate_from_prompt(self, tokens: Sequence[int], n_tokens: int) -> List[int]:

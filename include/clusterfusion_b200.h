@@ -275,6 +275,21 @@ int cf_decoder_tail(int64_t handle, void* stream);
 int cf_decoder_select_token(int64_t handle, const float* pairs_val, const int* pairs_idx, void* stream);
 int cf_decoder_destroy(int64_t handle);
 
+/* -------------------------------------------------------------------------
+ * Prompt ingestion.  The reference has no prefill kernel: its end-to-end
+ * scripts run the prompt through the HuggingFace model and copy the caches
+ * over (tests/benchmark_full.py:195-199, tests/benchmark_decode_6b9.py:40-50).
+ * This is the linear layer of that pass as a tensor-core GEMM:
+ *   out[m, n] = act(x[m, k] . weight[n, k]^T + bias[n] + residual[m, n])
+ * all fp16, fp32 accumulation; bias and residual may be NULL; residual only
+ * with CF_ACT_NONE.  n and k must be multiples of 8.  Asynchronous on `stream`.
+ * ------------------------------------------------------------------------- */
+#define CF_ACT_NONE 0
+#define CF_ACT_GELU_TANH 1
+#define CF_ACT_GELU_ERF 2
+int cf_prefill_linear(const void* x, const void* weight, const void* bias, const void* residual, void* out,
+                      int64_t m, int64_t n, int64_t k, int act, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
