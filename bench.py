@@ -314,6 +314,79 @@ def run_ours(args, rank, world):
         dist.destroy_process_group()
 
 
+def tensor_peak():
+    """(TFLOP/s, source): the measured cuBLAS bf16 burst figure of this pool if the driver left one."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json, burst)"
+    except Exception:
+        return 1590.0, "fallback (1.59 PFLOP/s)"
+
+
+def run_prefill(args):
+    """Secondary line: prompt ingestion of --prefill-tokens positions through PythiaDecoder.prefill()
+    (tensor-core GEMMs of this library + torch LayerNorm / RoPE / causal attention), and the four
+    linear layers of a block timed alone for the tensor roofline."""
+    import clusterfusionplus_b200 as cf
+    from clusterfusionplus_b200.decoder import prefill_linear
+    from clusterfusionplus_b200._lib import CF_ACT_GELU_TANH, CF_ACT_NONE, CfDims
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    m = args.prefill_tokens
+    H, NH, D, R, F, V = SHAPES[args.model]
+    args.ctx = 0
+    layers, head, caches, _ = build_model(args, dev, 0, 1)
+    max_seq = caches[0][0].shape[0]
+    if m + 1 > max_seq:
+        caches = [(torch.zeros(m + 8, NH * D, dtype=torch.float16, device=dev),
+                   torch.zeros(m + 8, NH * D, dtype=torch.float16, device=dev)) for _ in layers]
+        max_seq = m + 8
+    d = CfDims()
+    d.hidden, d.heads, d.head_dim, d.rotary, d.ffn, d.vocab = H, NH, D, R, F, V
+    dec = cf.PythiaDecoder(d, layers, head, caches, max_seq, use_graph=False)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(7)
+    prompt = torch.randint(0, V, (m + 1,), generator=g).tolist()  # prefill() leaves the last token to decode
+
+    def timed(fn, reps, warm):
+        for _ in range(warm):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ms_pass = timed(lambda: dec.prefill(prompt), args.steps, args.warmup)
+    w = layers[0]
+    x = rand_half((m, H), torch.Generator(device=dev), dev, std=1.0)
+    xf = rand_half((m, F), torch.Generator(device=dev), dev, std=1.0)
+    gemms = [(x, w["qkv_weight"], w["qkv_bias"], None, CF_ACT_NONE), (x, w["o_weight"], w["o_bias"], x, CF_ACT_NONE),
+             (x, w["mlp_up_weight"], w["mlp_up_bias"], None, CF_ACT_GELU_TANH),
+             (xf, w["mlp_down_weight"], w["mlp_down_bias"], x, CF_ACT_NONE)]
+    ms_gemm = timed(lambda: [prefill_linear(*a) for a in gemms], max(args.steps, 5), args.warmup)
+    flops = 2.0 * m * (3 * H * H + H * H + 2 * H * F)
+    peak, src = tensor_peak()
+    tf = flops / (ms_gemm * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "prompt ingestion throughput (tokens/s)", "value": m / (ms_pass * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_pass, "higher_is_better": True,
+        "dtype": "fp16 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"pythia-{args.model} shapes, {args.layers} layers, prompt of {m} tokens, batch 1"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "peak_source": src, "kernel": "the four linear layers of one block (QKV, O, MLP up + GELU, MLP down)",
+                     "ms_per_block": ms_gemm, "traffic": None},
+        "gemm_share_of_pass": ms_gemm * args.layers / ms_pass,
+        "device_status": cf.device_status(),
+    }))
+    dec.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,8 +400,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N > 1: in-kernel all-reduce over peer memory (default) or one NCCL all-reduce per layer")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="instead of decode: time prompt ingestion of this many tokens (1 GPU; a secondary line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.prefill_tokens > 0:
+        run_prefill(args)
+        return
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
