@@ -190,6 +190,25 @@ def llama_decoder_layer_sglang(input, residual, weight_qkv, weight_o, k_cache, v
     return out, residual, k, v
 
 
+def llama_mlp_sglang(input, residual, gate_up_weight, down_weight, rms_weight, eps):
+    """(output[1,4096], residual[1,4096]) of the SwiGLU MLP block of a Llama-2-7B layer, same conventions as
+    llama_decoder_layer_sglang: `residual` becomes input + residual in place, output =
+    down(silu(gate(y)) * up(y)) with y = RMSNorm(residual).  gate_up_weight is [2*ffn, 4096] (gate rows
+    first), down_weight [4096, ffn].  The reference leaves this block to the caller
+    (tests/test_llama.py:108-110)."""
+    H = 4096
+    ffn = int(down_weight.shape[-1])
+    opts = dict(dtype=torch.float16, device=input.device)
+    out = torch.empty((1, H), **opts)
+    res_out = torch.empty((1, H), **opts)
+    check(lib.cf_llama_mlp_sglang(
+        _req(input, "input", H), _req(residual, "residual", H), _req(gate_up_weight, "gate_up_weight", 2 * ffn * H),
+        _req(down_weight, "down_weight", H * ffn), _req(rms_weight, "rms_weight", H), float(eps), ffn,
+        out.data_ptr(), res_out.data_ptr(), _stream()))
+    residual.copy_(res_out.view_as(residual))
+    return out, residual
+
+
 # ---------------------------------------------------------------------------- contexts
 class _DeviceView:
     """Zero-copy torch view of a buffer the C library owns."""

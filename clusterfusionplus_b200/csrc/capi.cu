@@ -169,7 +169,7 @@ const void* kernel_ptr(int D, int cs) {
 struct DescKey {
     const void* p[14];
     int64_t kv_rows;
-    int dims[5];
+    int dims[6];
     bool operator<(const DescKey& o) const { return memcmp(this, &o, sizeof(DescKey)) < 0; }
 };
 
@@ -333,7 +333,8 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     }
     {
         // joint QKV + MLP-up row split: usable when the derived up ranges are monotone
-        const int ngq = 3 * d.heads * d.head_dim / GRAN, ng1 = ngq + d.ffn / GRAN;
+        const int ngq = (p.arch_flags & AF_NO_QKV) ? 0 : 3 * d.heads * d.head_dim / GRAN;
+        const int ng1 = ngq + (p.F_up ? p.F_up : d.ffn) / GRAN;
         bool ok = true;
         int prev = 0;
         for (int i = 1; i <= c.grid && ok; ++i) {
@@ -428,12 +429,12 @@ void base_params(Params& p, const CfDims& d, const Workspace& ws) {
 
 // Build the six tensor maps + pointers of one layer.  Null matrices are skipped.
 int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, void* k_cache, void* v_cache,
-                     int64_t kv_rows) {
+                     int64_t kv_rows, int up_rows = 0) {
     memset(&L, 0, sizeof(L));
     const int KVW = d.heads * d.head_dim;
     int rc;
     if (w.qkv_weight && (rc = encode_weight(&L.tm_qkv, w.qkv_weight, d.hidden, 3 * KVW))) return rc;
-    if (w.mlp_up_weight && (rc = encode_weight(&L.tm_up, w.mlp_up_weight, d.hidden, d.ffn))) return rc;
+    if (w.mlp_up_weight && (rc = encode_weight(&L.tm_up, w.mlp_up_weight, d.hidden, up_rows ? up_rows : d.ffn))) return rc;
     if (w.o_weight && (rc = encode_weight(&L.tm_o, w.o_weight, KVW, d.hidden))) return rc;
     if (w.mlp_down_weight && (rc = encode_weight(&L.tm_down, w.mlp_down_weight, d.ffn, d.hidden))) return rc;
     // a head's slice of a cache row is head_dim * 2 bytes: promote L2 fetches to 256 B only when
@@ -458,7 +459,7 @@ int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, voi
 
 // device-resident descriptor for an eager call; built once per distinct tensor set
 int cached_desc(DeviceState& ds, const CfDims& d, const CfLayerWeights& w, void* k_cache, void* v_cache,
-                int64_t kv_rows, cudaStream_t st, LayerDesc** out) {
+                int64_t kv_rows, cudaStream_t st, LayerDesc** out, int up_rows = 0) {
     DescKey key;
     memset(&key, 0, sizeof(key));
     const void* ptrs[14] = {w.qkv_weight, w.qkv_bias, w.o_weight, w.o_bias, w.ln_weight, w.ln_bias, w.post_ln_weight,
@@ -467,6 +468,7 @@ int cached_desc(DeviceState& ds, const CfDims& d, const CfLayerWeights& w, void*
     memcpy(key.p, ptrs, sizeof(ptrs));
     key.kv_rows = kv_rows;
     key.dims[0] = d.hidden; key.dims[1] = d.heads; key.dims[2] = d.head_dim; key.dims[3] = d.ffn; key.dims[4] = d.rotary;
+    key.dims[5] = up_rows;
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = ds.desc_cache.find(key);
     if (it != ds.desc_cache.end()) {
@@ -480,7 +482,7 @@ int cached_desc(DeviceState& ds, const CfDims& d, const CfLayerWeights& w, void*
         ds.desc_cache.clear();
     }
     LayerDesc host;
-    int rc = build_layer_desc(host, d, w, k_cache, v_cache, kv_rows);
+    int rc = build_layer_desc(host, d, w, k_cache, v_cache, kv_rows, up_rows);
     if (rc != CF_OK) return rc;
     LayerDesc* dev = nullptr;
     CF_CUDA(cudaMalloc(&dev, sizeof(LayerDesc)));
@@ -851,6 +853,42 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
     p.cos = cos;
     p.sin = sin;
     p.seq_host = static_cast<int>(seq_len);
+    return launch(*ds, d, p, st);
+}
+
+int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
+                        const void* rms_weight, float eps, int64_t ffn, void* output, void* residual_out, void* stream) {
+    if (!input || !gate_up_weight || !down_weight || !rms_weight || !output || !residual_out)
+        return fail(CF_ERR_INVALID, "null pointer");
+    if (residual && residual == residual_out) return fail(CF_ERR_INVALID, "residual_out must not alias residual");
+    if (ffn <= 0 || (ffn % GRAN) != 0 || 2 * ffn > WS_MAX_F)
+        return fail(CF_ERR_INVALID, "ffn %lld must be a positive multiple of %d and at most %d", (long long)ffn, GRAN, WS_MAX_F / 2);
+    const CfDims d = {4096, 32, 128, 128, static_cast<int>(ffn), 0};  // hidden of include/5090/llama/config.h:1-4
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CfLayerWeights w;
+    memset(&w, 0, sizeof(w));
+    w.mlp_up_weight = gate_up_weight;
+    w.mlp_down_weight = down_weight;
+    w.ln_weight = rms_weight;
+    LayerDesc* desc;
+    if ((rc = cached_desc(*ds, d, w, nullptr, nullptr, 0, st, &desc, 2 * d.ffn))) return rc;
+    Params p;
+    base_params(p, d, ds->ws);
+    p.layers = desc;
+    p.n_layers = 1;
+    p.phase_mask = PH_P1 | PH_P3;
+    p.p3_flags = F3_USE_DOWN;
+    p.arch_flags = AF_RMS_ADD | AF_NO_QKV | AF_SWIGLU;
+    p.F_up = 2 * d.ffn;
+    p.norm_eps = eps;
+    p.x_in = static_cast<const __half*>(input);
+    p.residual_in = static_cast<const __half*>(residual);
+    p.residual_out = static_cast<__half*>(residual_out);
+    p.out = static_cast<__half*>(output);
+    p.seq_host = 0;
     return launch(*ds, d, p, st);
 }
 

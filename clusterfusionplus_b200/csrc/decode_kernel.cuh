@@ -67,6 +67,8 @@ enum : int {
     AF_QKV_PLANAR = 2,  // QKV weight rows are [Q of all heads; K of all heads; V of all heads]
     AF_NO_APPEND = 4,   // the caches hold exactly seq_len rows and are not written
     AF_GELU_ERF = 8,    // MLP activation is the exact GELU x * Phi(x) instead of the tanh form
+    AF_NO_QKV = 16,     // P1 streams the MLP-up matrix only (an MLP block on its own)
+    AF_SWIGLU = 32,     // the up matrix is [gate rows; up rows] (F_up = 2F, no bias); mid = silu(gate) * up
 };
 enum : int {
     F3_USE_O = 1,       // include W_o chunks (attention output) in P3
@@ -150,6 +152,7 @@ struct Params {
     int p1_joint;      // P1 row split: 1 = every CTA QKV share then up share, jointly balanced (host verified it
                        // is monotone), 0 = the same with independent even splits, 2 = grouped (QKV CTAs, up CTAs)
     int gq;            // grouped split: CTAs in the QKV group
+    int F_up;          // rows of the MLP-up matrix when they are not F (AF_SWIGLU: 2F); 0 = F
     int arch_flags;    // AF_*
     float norm_eps;    // RMSNorm epsilon (AF_RMS_ADD)
     const __half* residual_in;  // [H], AF_RMS_ADD
@@ -910,7 +913,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
     // ---- static work split (identical on producer and consumer side)
     const int KC1 = ceil_div(H, KCHUNK);
-    const int NGq = (3 * KVW) / GRAN, NGu = F / GRAN, NG1 = NGq + NGu;
+    const int NGq = (p.arch_flags & AF_NO_QKV) ? 0 : (3 * KVW) / GRAN;
+    const int NGu = (p.F_up ? p.F_up : F) / GRAN, NG1 = NGq + NGu;
     // Every CTA streams a share of the QKV rows first and a share of the MLP-up rows after it, as
     // one sequence of granules.  The up share is cut so that QKV + up together are as even as the
     // grid allows (p1_joint, verified by the host); otherwise each is split evenly on its own.
@@ -1331,7 +1335,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     __half* dm16 = p.mid_f16_out;
                     const int rowq0 = qa * GRAN, rowu0 = ua * GRAN;
                     co.rows_phase2(
-                        qb - qa, ub - ua, KC1, sm.xbuf, sm.xbuf + H,
+                        qb - qa, ub - ua, KC1, sm.xbuf, (p.arch_flags & AF_RMS_ADD) ? sm.xbuf : sm.xbuf + H,
                         [&](int g, int r, float v) {
                             const int row = rowq0 + g * GRAN + r;
                             const float out = bq ? v + __half2float(__ldg(bq + row)) : v;
@@ -1346,6 +1350,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         },
                         [&](int g, int r, float v) {
                             const int row = rowu0 + g * GRAN + r;
+                            if (p.arch_flags & AF_SWIGLU) {  // raw gate / up values; combined where P3 stages them
+                                dm[row] = v;
+                                return;
+                            }
                             const float pre = v + __half2float(__ldg(bu + row));
                             const float a = (p.arch_flags & AF_GELU_ERF) ? gelu_erf_f(pre) : gelu_tanh_f(pre);
                             dm[row] = a;
@@ -1567,7 +1575,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 // them while the GEMV already runs over the MLP chunks.
                 const int nmid = my3 - nattn;
                 if (tid == 0) mbar_arrive(smem_u32(sm.h_go));
-                if (!(p.p3_flags & F3_MID_F16)) {
+                if (p.arch_flags & AF_SWIGLU) {
+                    // mid[e] = silu(gate[e]) * up[e], gate rows at [0, F), up rows at [F, 2F) of the scratch
+                    const int nvec = nmid * (KCHUNK / 4);
+                    for (int v0 = tid; v0 < nvec; v0 += NCTHR * 4) {
+                        float4 gv[4], uv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int v = v0 + u * NCTHR;
+                            gv[u] = uv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (v < nvec) {
+                                const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                                const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;  // F is a multiple of 8
+                                if (e < F) {
+                                    gv[u] = ld_cg_f32x4(p.mid_f32 + e);
+                                    uv[u] = ld_cg_f32x4(p.mid_f32 + F + e);
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int v = v0 + u * NCTHR;
+                            if (v < nvec) {
+                                const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                                float4 o;
+                                o.x = gv[u].x / (1.f + __expf(-gv[u].x)) * uv[u].x;
+                                o.y = gv[u].y / (1.f + __expf(-gv[u].y)) * uv[u].y;
+                                o.z = gv[u].z / (1.f + __expf(-gv[u].z)) * uv[u].z;
+                                o.w = gv[u].w / (1.f + __expf(-gv[u].w)) * uv[u].w;
+                                *reinterpret_cast<float4*>(sm.xbuf + i * KCHUNK + k4 * 4) = o;
+                            }
+                        }
+                    }
+                } else if (!(p.p3_flags & F3_MID_F16)) {
                     // asynchronous 16-byte copies of the fp32 intermediate straight into xbuf
                     const int nvec = nmid * (KCHUNK / 4);
                     for (int v = tid; v < nvec; v += NCTHR) {

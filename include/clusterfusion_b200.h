@@ -136,6 +136,15 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
                                   const void* rms_input_weight, float eps, const float* cos, const float* sin,
                                   void* output, void* residual_out, void* k_new, void* v_new, void* stream);
 
+/* The SwiGLU MLP block that follows the attention block in a Llama-2-7B layer, with the same
+ * fused-add front:  residual_out = input + residual (fp16);  y = RMSNorm(residual_out, eps) * rms_weight;
+ * output = (silu(y Wg^T) * (y Wu^T)) Wd^T.   gate_up_weight is [2*ffn, 4096] with the gate rows first
+ * (the merged gate_up_proj of serving stacks), down_weight [4096, ffn]; no biases.  `residual` may be
+ * NULL.  The reference's Llama kernels stop after the attention block and leave this block to the
+ * caller (tests/test_llama.py:108-110 has it commented out); BASELINE config 5 counts it. */
+int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
+                        const void* rms_weight, float eps, int64_t ffn, void* output, void* residual_out, void* stream);
+
 /* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
  * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one
  * launch, reading what earlier phases left in the library's scratch.  Used by the

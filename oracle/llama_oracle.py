@@ -76,3 +76,40 @@ def hf_llama_attn_block(x, residual, weight_qkv, weight_o, k_cache, v_cache, rms
         out = attn(norm(s).reshape(1, 1, H), position_embeddings=pe, attention_mask=None, past_key_values=cache)[0]
     return out.reshape(1, H), s, cache.layers[0].keys[:, :, -1].reshape(1, heads, head_dim), \
         cache.layers[0].values[:, :, -1].reshape(1, heads, head_dim)
+
+
+def llama_mlp_block_fp32(x, residual, gate_up_weight, down_weight, rms_weight, eps):
+    """The SwiGLU MLP block with the fused-add front (same conventions as llama_attn_block_fp32):
+    s = fp16(x + residual); y = RMSNorm(s) * rms_weight; out = (silu(y Wg^T) * (y Wu^T)) Wd^T.
+    gate_up_weight [2F, H], gate rows first; down_weight [H, F].  Returns (out [1,H], s [1,H]) fp32.
+    The reference's own test keeps this block as commented-out torch code (tests/test_llama.py:108-110);
+    the arithmetic is LlamaMLP's (transformers/models/llama/modeling_llama.py)."""
+    f = lambda t: t.detach().to("cpu", torch.float32)
+    H = f(x).numel()
+    F = down_weight.shape[-1]
+    s = (f(x).reshape(1, H) + f(residual).reshape(1, H)).to(torch.float16).to(torch.float32)
+    y = s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + eps) * f(rms_weight).reshape(-1)
+    gu = y @ f(gate_up_weight).t()
+    mid = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    return mid @ f(down_weight).t(), s
+
+
+def hf_llama_mlp_block(x, residual, gate_up_weight, down_weight, rms_weight, eps):
+    """The same block through transformers' LlamaRMSNorm + LlamaMLP in fp32."""
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaMLP, LlamaRMSNorm
+    f = lambda t: t.detach().to("cpu", torch.float32)
+    H = f(x).numel()
+    F = down_weight.shape[-1]
+    cfg = LlamaConfig(hidden_size=H, intermediate_size=F, num_attention_heads=max(1, H // 128), num_hidden_layers=1,
+                      rms_norm_eps=eps, vocab_size=32, hidden_act="silu", mlp_bias=False)
+    norm = LlamaRMSNorm(H, eps=eps).float()
+    mlp = LlamaMLP(cfg).float().eval()
+    W = f(gate_up_weight)
+    with torch.no_grad():
+        norm.weight.copy_(f(rms_weight).reshape(-1))
+        mlp.gate_proj.weight.copy_(W[:F])
+        mlp.up_proj.weight.copy_(W[F:])
+        mlp.down_proj.weight.copy_(f(down_weight))
+        s = (f(x).reshape(1, H) + f(residual).reshape(1, H)).to(torch.float16).to(torch.float32)
+        return mlp(norm(s)), s

@@ -63,3 +63,49 @@ def test_llama_deterministic_and_checked(cuda_device):
     with pytest.raises(RuntimeError):
         cf.llama_decoder_layer_sglang(t["x"], t["res"], t["wqkv"], t["wo"], t["k"][:0], t["v"][:0], t["g"], 1e-6,
                                       t["cos"], t["sin"])
+
+
+def make_mlp(ffn, dev, seed=7):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rw = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.1).half()
+    # weights at the scale of a trained model keep |out| ~ 1, where the absolute tolerance means something
+    rs = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.02).half()
+    return dict(x=rw(1, H), res=rw(1, H), wgu=rs(2 * ffn, H), wd=rs(H, ffn), g=(1 + 0.1 * torch.randn(1, H, generator=g, device=dev)).half())
+
+
+@pytest.mark.parametrize("ffn", [11008, 8192, 2048, 5504])
+def test_llama_mlp_block_vs_oracle(cuda_device, ffn):
+    import clusterfusion as cf
+    t = make_mlp(ffn, cuda_device)
+    res_in = t["res"].clone()
+    out, res = cf.llama_mlp_sglang(t["x"], t["res"], t["wgu"], t["wd"], t["g"], 1e-5)
+    assert cf.device_status() == 0
+    assert res.data_ptr() == t["res"].data_ptr()
+    ro, rr = L.llama_mlp_block_fp32(t["x"], res_in, t["wgu"], t["wd"], t["g"], 1e-5)
+    assert torch.equal(res.float().cpu(), rr)
+    assert_close(out, ro, "mlp output")
+    again, _ = cf.llama_mlp_sglang(t["x"], res_in.clone(), t["wgu"], t["wd"], t["g"], 1e-5)
+    assert torch.equal(out, again)                         # deterministic
+
+
+def test_llama_layer_stack_two_layers_vs_oracle(cuda_device):
+    """Attention block then MLP block, twice, with the (hidden, residual) hand-over serving stacks use."""
+    import clusterfusion as cf
+    seq, ffn = 300, 11008
+    layers = [(make(seq, cuda_device, seed=20 + i), make_mlp(ffn, cuda_device, seed=30 + i)) for i in range(2)]
+    for a, _ in layers:  # trained-model scale for the attention weights too
+        a["wqkv"] = (a["wqkv"].float() * 0.2).half()
+        a["wo"] = (a["wo"].float() * 0.2).half()
+    x = layers[0][0]["x"].clone()
+    res = layers[0][0]["res"].clone()
+    xo, ro = x.clone(), res.clone()
+    for a, m in layers:
+        x, res, _, _ = cf.llama_decoder_layer_sglang(x, res, a["wqkv"], a["wo"], a["k"], a["v"], a["g"], 1e-5, a["cos"], a["sin"])
+        x, res = cf.llama_mlp_sglang(x, res, m["wgu"], m["wd"], m["g"], 1e-5)
+        xo, ro, _, _ = L.llama_attn_block_fp32(xo, ro, a["wqkv"], a["wo"], a["k"], a["v"], a["g"], 1e-5, a["cos"], a["sin"])
+        xo = xo.half()
+        xo, ro = L.llama_mlp_block_fp32(xo, ro, m["wgu"], m["wd"], m["g"], 1e-5)
+        xo = xo.half()
+    assert cf.device_status() == 0
+    assert_close(x, xo.float(), "stack output")
+    assert_close(res, ro, "stack residual")

@@ -106,3 +106,16 @@ def test_llama_oracle_matches_hf_attention():
     b = L.hf_llama_attn_block(x, r, wq, wo, k, v, g, 1e-6, cos, sin, NH, D)
     for p, q in zip(a, b):
         assert O.compare(p, q)[0] < 1e-5
+
+
+def test_llama_mlp_oracle_matches_hf_mlp():
+    """Pins the SwiGLU MLP restatement against transformers' LlamaRMSNorm + LlamaMLP (fp32)."""
+    from oracle import llama_oracle as L
+    g = torch.Generator().manual_seed(11)
+    H, F = 512, 1408
+    rw = lambda *shape: (torch.randn(*shape, generator=g) * 0.1).half()
+    x, r, wgu, wd, gm = rw(1, H), rw(1, H), rw(2 * F, H), rw(H, F), rw(1, H)
+    a = L.llama_mlp_block_fp32(x, r, wgu, wd, gm, 1e-6)
+    b = L.hf_llama_mlp_block(x, r, wgu, wd, gm, 1e-6)
+    assert torch.equal(a[1], b[1])
+    assert torch.allclose(a[0], b[0], atol=1e-5, rtol=1e-5)
