@@ -387,6 +387,69 @@ def run_prefill(args):
     dec.close()
 
 
+def run_llama_stack(args):
+    """Secondary line: one decode step at batch 1 through a Llama-2-7B-shaped stack of --layers layers
+    (attention block + SwiGLU MLP block per layer, 64 launches replayed as one CUDA graph), every
+    layer with its own --llama-ctx rows of KV cache."""
+    import clusterfusionplus_b200 as cf
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    H, NH, D, F, S, L = 4096, 32, 128, 11008, args.llama_ctx, args.layers
+    g = torch.Generator(device=dev)
+    g.manual_seed(4321)
+    layers = []
+    for _ in range(L):
+        layers.append(dict(
+            weight_qkv=rand_half((3 * H, H), g, dev), weight_o=rand_half((H, H), g, dev),
+            rms_input_weight=rand_half((H,), g, dev, 1.0), k_cache=rand_half((S, H), g, dev, std=1.0),
+            v_cache=rand_half((S, H), g, dev, std=1.0), gate_up_weight=rand_half((2 * F, H), g, dev),
+            down_weight=rand_half((H, F), g, dev), rms_post_weight=rand_half((H,), g, dev, 1.0)))
+    ang = torch.rand(D // 2, generator=g, device=dev) * (2 * torch.pi)
+    cos, sin = torch.cat([ang.cos(), ang.cos()]).contiguous(), torch.cat([ang.sin(), ang.sin()]).contiguous()
+    x0, r0 = rand_half((1, H), g, dev, std=1.0), rand_half((1, H), g, dev, std=1.0)
+    stack = cf.LlamaLayerStack(layers, eps=1e-5)
+
+    def step():
+        stack.step(x0, r0, cos, sin)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()  # builds the per-layer descriptors (allocations) outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    sampler = ClockSampler(0)
+    for _ in range(args.warmup):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.summary(t0, time.perf_counter())
+    us = e0.elapsed_time(e1) / args.steps * 1e3
+    per_layer = 2 * (3 * H * H + H * H + 3 * H * F) + 2 * 2 * S * H + 2 * (2 * H) + 2 * 2 * H * 4  # weights, KV, norms, x/res in-out
+    peak, src = hbm_peak()
+    gbs = per_layer * L / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "Llama-2-7B-shaped layer stack, B=1 decode step (us)", "value": us, "unit": "us/token", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
+        "dtype": "fp16 weights/KV, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{L} layers x (attention block + SwiGLU MLP 4096-11008-4096), batch 1, {S} cached rows per layer",
+                   "l2": "per-step working set far larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": src,
+                     "algorithmic_bytes_per_step": per_layer * L, "traffic": None},
+        "gpu_launches": 2 * L * args.steps, "clocks": clocks, "device_status": cf.device_status(),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -400,12 +463,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N > 1: in-kernel all-reduce over peer memory (default) or one NCCL all-reduce per layer")
+    ap.add_argument("--llama-ctx", type=int, default=0,
+                    help="instead of Pythia decode: one step through a Llama-2-7B-shaped layer stack with this many "
+                         "cached rows per layer (1 GPU, batch 1; a secondary line)")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="instead of decode: time prompt ingestion of this many tokens (1 GPU; a secondary line)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.prefill_tokens > 0:
         run_prefill(args)
+        return
+    if args.llama_ctx > 0:
+        run_llama_stack(args)
         return
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

@@ -109,3 +109,22 @@ def test_llama_layer_stack_two_layers_vs_oracle(cuda_device):
     assert cf.device_status() == 0
     assert_close(x, xo.float(), "stack output")
     assert_close(res, ro, "stack residual")
+
+
+def test_llama_layer_stack_class_matches_block_calls(cuda_device):
+    """LlamaLayerStack (ping-pong buffers, no copies) gives bit-identical results to chaining the two block calls."""
+    import clusterfusion as cf
+    seq, ffn = 129, 11008
+    blocks = [(make(seq, cuda_device, seed=40 + i), make_mlp(ffn, cuda_device, seed=50 + i)) for i in range(3)]
+    layers = [dict(weight_qkv=a["wqkv"], weight_o=a["wo"], rms_input_weight=a["g"], k_cache=a["k"], v_cache=a["v"],
+                   gate_up_weight=m["wgu"], down_weight=m["wd"], rms_post_weight=m["g"]) for a, m in blocks]
+    a0 = blocks[0][0]
+    stack = cf.LlamaLayerStack(layers, eps=1e-5)
+    xs, rs = stack.step(a0["x"], a0["res"], a0["cos"], a0["sin"])
+    x, res = a0["x"].clone(), a0["res"].clone()
+    for i, (a, m) in enumerate(blocks):
+        x, res, kn, vn = cf.llama_decoder_layer_sglang(x, res, a["wqkv"], a["wo"], a["k"], a["v"], a["g"], 1e-5, a0["cos"], a0["sin"])
+        assert torch.equal(kn[0], stack.k_new[i]) and torch.equal(vn[0], stack.v_new[i])
+        x, res = cf.llama_mlp_sglang(x, res, m["wgu"], m["wd"], m["g"], 1e-5)
+    assert torch.equal(x, xs) and torch.equal(res, rs)
+    assert cf.device_status() == 0
