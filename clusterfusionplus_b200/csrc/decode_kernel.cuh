@@ -178,6 +178,9 @@ struct TpLayout {
     __host__ __device__ size_t bytes() const { return pairs_off(2, 0); }
 };
 
+// pause between re-reads of a word in global memory that has not arrived yet
+constexpr int POLL_BACKOFF_NS = 96;
+
 __device__ __forceinline__ void st_ll(void* p, unsigned bits, unsigned epoch) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(epoch) : "memory");
 }
@@ -195,7 +198,7 @@ __device__ __forceinline__ uint4 ld_ll2(const void* p) {
 // wait (bounded) until the word at p carries `epoch`; returns its payload bits
 __device__ __forceinline__ unsigned wait_ll(const void* p, unsigned epoch, const AbortCtl& ab) {
     uint2 v = ld_ll(p);
-    if (v.y != epoch) wait_bounded([&] { v = ld_ll(p); return v.y == epoch; }, ab, ST_TIMEOUT_PEER);
+    if (v.y != epoch) wait_bounded<POLL_BACKOFF_NS>([&] { v = ld_ll(p); return v.y == epoch; }, ab, ST_TIMEOUT_PEER);
     return v.x;
 }
 
@@ -402,7 +405,7 @@ __device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned& epoch,
         const unsigned target = epoch * G;
         __threadfence();
         atomicAdd(counter, 1u);
-        wait_bounded([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
+        wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
         __threadfence();
     }
     consumer_sync(NCTHR);
@@ -421,7 +424,7 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter, unsigned& epoch, 
 __device__ __forceinline__ void grid_wait(unsigned* counter, unsigned epoch, unsigned G, int tid, const AbortCtl& ab) {
     if (tid == 0) {
         const unsigned target = epoch * G;
-        wait_bounded([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
+        wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(counter) >= target; }, ab, ST_TIMEOUT_GRID);
         __threadfence();
     }
     consumer_sync(NCTHR);
@@ -542,7 +545,7 @@ __device__ __forceinline__ void layer_norm2_to_smem(const __half* x, const uint2
         const int v = j * NCTHR + tid;
         if (v < nvec && xll) {
             uint4 w[4];
-            wait_bounded(
+            wait_bounded<POLL_BACKOFF_NS>(
                 [&] {
                     bool ok = true;
 #pragma unroll
@@ -1039,7 +1042,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         auto watch_mid = [&](int l) {
             if (mid_wait && ht == 0) {
                 const unsigned target = static_cast<unsigned>(l + 1) * static_cast<unsigned>(G);
-                wait_bounded([&] { return ld_acquire_u32(p.sync + 3) >= target; }, ab, ST_TIMEOUT_GRID);
+                wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(p.sync + 3) >= target; }, ab, ST_TIMEOUT_GRID);
                 __threadfence();
                 mbar_arrive(smem_u32(sm.mid_ready));
             }
@@ -1090,7 +1093,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                     return ok;
                 };
-                if (!fetch()) wait_bounded(fetch, ab, ST_TIMEOUT_PEER);
+                if (!fetch()) wait_bounded<POLL_BACKOFF_NS>(fetch, ab, ST_TIMEOUT_PEER);
 #pragma unroll
                 for (int k = 0; k < KQ; ++k) {
                     const int e = ht + k * NHTHR;
@@ -1169,7 +1172,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (!p.part_any_epoch) {
                                 const unsigned* ew = reinterpret_cast<const unsigned*>(pbase + o + D + 2);
                                 if (ld_acquire_u32(ew) != pep)
-                                    wait_bounded([&] { return ld_acquire_u32(ew) == pep; }, ab, ST_TIMEOUT_GRID);
+                                    wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(ew) == pep; }, ab, ST_TIMEOUT_GRID);
                             }
                             mreg[k] = ld_cg_f32(pbase + o + D);
                             lreg[k] = ld_cg_f32(pbase + o + D + 1);
@@ -1694,13 +1697,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (r != p.tp_rank)
                                 st_ll(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(row) * 8,
                                       __float_as_uint(mine), tp_epoch);
+                        // all counterparts' words in flight at once; re-read (bounded) until every epoch matches
+                        const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(row) * 8;
+                        uint2 w[MAX_TP];
+                        auto fetch = [&]() {
+                            bool ok = true;
+#pragma unroll
+                            for (int r = 0; r < MAX_TP; ++r) {
+                                if (r < p.tp_size && r != p.tp_rank) {
+                                    w[r] = ld_ll(mybuf + tl.partial_off(parity, r));
+                                    ok = ok && (w[r].y == tp_epoch);
+                                }
+                            }
+                            return ok;
+                        };
+                        if (!fetch()) wait_bounded<POLL_BACKOFF_NS>(fetch, ab, ST_TIMEOUT_PEER);
                         float sum = 0.f;
-                        for (int r = 0; r < p.tp_size; ++r) {
-                            const float v = (r == p.tp_rank)
-                                ? mine
-                                : __uint_as_float(wait_ll(p.tp_peer[p.tp_rank] + tl.partial_off(parity, r) + static_cast<size_t>(row) * 8, tp_epoch, ab));
-                            sum += v;
-                        }
+#pragma unroll
+                        for (int r = 0; r < MAX_TP; ++r)
+                            if (r < p.tp_size) sum += (r == p.tp_rank) ? mine : __uint_as_float(w[r].x);
                         store_y(row, sum + epi_add);
                     }
                 }

@@ -90,14 +90,18 @@ __device__ __forceinline__ void raise_abort(const AbortCtl& a, int code) {
 
 // Spin on `probe()` until it returns true, the CTA has aborted, or the time
 // limit passes.  Returns false when the wait was abandoned.
-template <class Probe>
+// BACKOFF_NS > 0 sleeps between probes: for polls of global memory, where many waiting threads
+// would otherwise load the L2 (and the data arriving over NVLink) with re-reads.
+template <int BACKOFF_NS = 0, class Probe>
 __device__ __forceinline__ bool wait_bounded(Probe probe, const AbortCtl& a, int code) {
     if (probe()) return true;
     if (*a.flag) return false;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t it = 0;
+    constexpr uint32_t CHECK_MASK = BACKOFF_NS > 0 ? 0xfu : 0xffu;
     while (!probe()) {
-        if ((++it & 0xffu) == 0) {
+        if constexpr (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
+        if ((++it & CHECK_MASK) == 0) {
             if (*a.flag) return false;
             if (globaltimer_ns() - t0 > wait_limit_ns(code)) {
                 raise_abort(a, code);
