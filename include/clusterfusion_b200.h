@@ -141,7 +141,7 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
  * output = (silu(y Wg^T) * (y Wu^T)) Wd^T.   gate_up_weight is [2*ffn, 4096] with the gate rows first
  * (the merged gate_up_proj of serving stacks), down_weight [4096, ffn]; no biases.  `residual` may be
  * NULL.  The reference's Llama kernels stop after the attention block and leave this block to the
- * caller (tests/test_llama.py:108-110 has it commented out); BASELINE config 5 counts it. */
+ * caller (tests/test_llama.py:108-110 has it commented out); a full Llama layer needs it. */
 int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
                         const void* rms_weight, float eps, int64_t ffn, void* output, void* residual_out, void* stream);
 

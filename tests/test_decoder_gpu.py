@@ -137,7 +137,7 @@ def _full_model_rollout(shape, prompt_len, steps, seed, dev):
 
 
 def test_pythia_2b8_greedy_64_steps_identical(cuda_device):
-    """BASELINE configuration 2 (full Pythia-2.8B, seeded random init, prompt of 128 random
+    """The full-model parity case (full Pythia-2.8B, seeded random init, prompt of 128 random
     ids): 64 greedy tokens identical to the fp32 oracle's."""
     got, want, gaps, (mx, rl), status = _full_model_rollout(O.PYTHIA_2B8, 128, 64, 31337, cuda_device)
     first_diff = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), None)
