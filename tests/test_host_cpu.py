@@ -71,6 +71,62 @@ def test_cpu_tensors_are_rejected():
         clusterfusion.pythia_2b8_decoder_layer(*args)
 
 
+def test_new_entry_points_validate_before_touching_the_device():
+    """Argument errors of the prefill GEMM and the Llama MLP block are reported with a message,
+    GPU or not; with good arguments and no GPU the call fails on the missing device."""
+    from clusterfusionplus_b200 import _lib
+    lib = _lib.lib
+    one = ctypes.c_void_p(16)  # never dereferenced: validation comes first
+    assert lib.cf_prefill_linear(one, one, None, None, one, 4, 1020, 1024, 0, None) != 0
+    assert "multiples of 8" in _lib.last_error()
+    assert lib.cf_prefill_linear(one, one, None, one, one, 4, 1024, 1024, _lib.CF_ACT_GELU_TANH, None) != 0
+    assert "residual" in _lib.last_error()
+    assert lib.cf_prefill_linear(one, one, None, None, one, 4, 1024, 1024, 9, None) != 0
+    assert "activation" in _lib.last_error()
+    assert lib.cf_prefill_linear(None, one, None, None, one, 4, 1024, 1024, 0, None) != 0
+    assert lib.cf_llama_mlp_sglang(one, None, one, one, one, 1e-5, 11007, one, one, None) != 0
+    assert "ffn" in _lib.last_error()
+    assert lib.cf_llama_mlp_sglang(one, one, one, one, one, 1e-5, 11008, one, one, None) != 0
+    assert "alias" in _lib.last_error()
+    if not torch.cuda.is_available():
+        assert lib.cf_prefill_linear(one, one, None, None, one, 4, 1024, 1024, 0, None) != 0
+        assert _lib.last_error() != ""
+
+
+def test_checkpoint_adaptor_edge_cases():
+    """Tied LM head, missing attention biases and a wrong tensor shape."""
+    import clusterfusionplus_b200 as cf
+    from transformers import GPTNeoXConfig
+    cfg = GPTNeoXConfig(hidden_size=256, num_attention_heads=2, intermediate_size=512, num_hidden_layers=1,
+                        vocab_size=64, rotary_pct=0.25, hidden_act="gelu_new")
+    d, flags, base = cf.describe_config(cfg)
+    assert (d.head_dim, d.rotary, flags) == (128, 32, 0)
+    H, F, V = 256, 512, 64
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g)
+    sd = {"gpt_neox.embed_in.weight": r(V, H), "gpt_neox.final_layer_norm.weight": r(H), "gpt_neox.final_layer_norm.bias": r(H)}
+    pre = "gpt_neox.layers.0."
+    sd.update({pre + "input_layernorm.weight": r(H), pre + "input_layernorm.bias": r(H),
+               pre + "post_attention_layernorm.weight": r(H), pre + "post_attention_layernorm.bias": r(H),
+               pre + "attention.query_key_value.weight": r(3 * H, H), pre + "attention.dense.weight": r(H, H),
+               pre + "mlp.dense_h_to_4h.weight": r(F, H), pre + "mlp.dense_h_to_4h.bias": r(F),
+               pre + "mlp.dense_4h_to_h.weight": r(H, F), pre + "mlp.dense_4h_to_h.bias": r(H)})
+    layers, head = cf.convert_state_dict(sd, cfg, device="cpu")
+    w = layers[0]
+    assert head["embed_out"] is head["embed_in"]                       # tied: no embed_out.weight in the dict
+    assert w["qkv_bias"].shape == (3 * H,) and not w["qkv_bias"].any()  # attention biases absent -> zeros
+    assert not w["o_bias"].any() and w["mlp_up_bias"].any()
+    assert all(t.dtype == torch.float16 and t.is_contiguous() for t in w.values())
+    assert torch.equal(w["qkv_weight"], sd[pre + "attention.query_key_value.weight"].half())
+    bad = dict(sd)
+    bad[pre + "mlp.dense_h_to_4h.weight"] = r(F + 8, H)
+    with pytest.raises(RuntimeError, match="shapes"):
+        cf.convert_state_dict(bad, cfg, device="cpu")
+    del bad[pre + "input_layernorm.weight"]
+    with pytest.raises(RuntimeError):
+        cf.convert_state_dict(bad, cfg, device="cpu")
+
+
 # ---- mirror of the kernel's static split (decode_kernel.cuh: part_begin / part_of)
 def part_begin(i, total, parts):
     return (i * total) // parts
