@@ -346,9 +346,9 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         // Pythia-6.9B on 1, 4 and 8 GPUs (0.4 - 6 %), ties on 2 GPUs, loses 1.5 % for Pythia-2.8B.
         p.p1_joint = 2;  // grouped; 1 / 0 (every CTA both matrices) stay selectable for experiments
         (void)ok;
-        // Grouped split: MLP-up CTAs count in at barrier 1 before they start (attention needs only q/k/v), so
-        // the barrier waits for the QKV group alone.  Give that group one granule per CTA less than the
-        // average: it finishes a barrier latency early and nobody waits.
+        // Grouped split: attention needs only q/k/v, which the QKV group produces.  Give that group one
+        // granule per CTA less than the average, so that q/k/v exist by the time the MLP-up group reaches
+        // attention and nobody polls for long.
         {
             // ... but never more than 10 % less, which matters for small shards
             const double avg = static_cast<double>(ng1) / c.grid;

@@ -10,21 +10,24 @@
 // but is organised differently:
 //
 //   P1  LayerNorm (both norms share mean/rstd) -> {QKV, MLP-up} GEMV, output rows
-//       partitioned over ALL CTAs (no split-K), + bias (+ tanh-GELU for MLP-up)
-//   --- grid barrier ---
+//       partitioned over ALL CTAs (no split-K), + bias (+ GELU for MLP-up)
 //   P2  partial NeoX RoPE, KV append, flash-decode over (head, 128-row chunk)
 //       items spread evenly over all CTAs, per-CTA partial (m, l, acc) in fp32
-//   --- grid barrier ---
 //   P3  merge attention partials, {O-proj, MLP-down} as ONE GEMV over
 //       K = [attn ; mid]; K-chunks interleaved over the CTAs of a cluster and
 //       the partial rows summed through distributed shared memory
 //       (dsm.cuh), + biases + residual -> fp16 output
 //   P4  (optional tail) final LayerNorm -> LM-head GEMV -> argmax
 //
+// There is no grid barrier between the phases of a layer nor between layers: what
+// one CTA hands to the others travels as epoch-tagged words or epoch-stamped records
+// that the readers poll (st_ll / publish_record below), and the MLP intermediate is
+// gated by a count of CTAs past P1.  Grid barriers remain in the tail only.
+//
 // One producer thread issues every TMA load of the whole launch in program
 // order, limited only by ring capacity: it runs ahead of the consumers across
 // phase and layer boundaries, so the next phase's weights are already landing
-// while the consumers sit in a grid barrier.
+// while the consumers wait for other CTAs' data.
 //
 // Determinism: no atomics on data; every sum has a fixed association order that
 // depends only on (grid size, cluster size, sequence length).
@@ -257,7 +260,7 @@ struct Smem {
     uint64_t* full;
     uint64_t* empty;
     uint64_t* xbar;
-    uint64_t* h_go;        // consumers -> helpers: the barrier before P3 has been passed
+    uint64_t* h_go;        // consumers -> helpers: this CTA has entered P3, xbuf's attention chunks are free
     uint64_t* attn_ready;  // helpers -> consumers: merged attention chunks are in xbuf
     uint64_t* mid_ready;   // helper thread -> consumers: every CTA is past P1, the MLP intermediate is complete
     uint64_t* h_layer;     // consumers -> helpers: a new layer has begun, xbuf's spare region is free
