@@ -17,6 +17,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import llama_oracle as L  # noqa: E402
 from oracle import pythia_oracle as O  # noqa: E402
 
 # (name, model, seq_len, weight seed, input seed)
@@ -40,6 +41,30 @@ def layer_case_inputs(model, seq_len, wseed, xseed, device="cpu"):
     k, v = O.make_kv_cache(s, seq_len, seq_len + 3, xseed + 100, device=device)
     cos, sin = O.rope_table(seq_len + 1, s.rotary, device=device)
     return s, w, x, k, v, cos[seq_len].contiguous(), sin[seq_len].contiguous()
+
+
+# Llama-2-7B blocks (hidden 4096, 32 heads x 128): (name, cached rows or ffn, seed)
+LLAMA_ATTN_CASES = [("llama_attn_seq65", 65, 501), ("llama_attn_seq1", 1, 502)]
+LLAMA_MLP_CASES = [("llama_mlp_ffn2048", 2048, 601), ("llama_mlp_ffn11008", 11008, 602)]
+LLAMA_EPS = 1e-5
+
+
+def llama_attn_inputs(seq, seed, device="cpu"):
+    """fp16 tensors of one attention-block call, regenerated from the seed."""
+    H, D = 4096, 128
+    n = lambda shape, i, std, mean=0.0: O.seeded_normal(shape, seed + i, mean=mean, std=std, device=device).half()
+    ang = torch.rand(D // 2, generator=torch.Generator().manual_seed(seed + 9)) * (2 * torch.pi)
+    return dict(x=n((1, H), 0, 1.0), res=n((1, H), 1, 1.0), wqkv=n((3 * H, H), 2, 0.02), wo=n((H, H), 3, 0.02),
+                k=n((seq, H), 4, 1.0), v=n((seq, H), 5, 1.0), g=n((1, H), 6, 0.1, 1.0),
+                cos=torch.cat([ang.cos(), ang.cos()]).contiguous().to(device),
+                sin=torch.cat([ang.sin(), ang.sin()]).contiguous().to(device))
+
+
+def llama_mlp_inputs(ffn, seed, device="cpu"):
+    H = 4096
+    n = lambda shape, i, std, mean=0.0: O.seeded_normal(shape, seed + i, mean=mean, std=std, device=device).half()
+    return dict(x=n((1, H), 0, 1.0), res=n((1, H), 1, 1.0), wgu=n((2 * ffn, H), 2, 0.02), wd=n((H, ffn), 3, 0.02),
+                g=n((1, H), 4, 0.1, 1.0))
 
 
 def checksum(*tensors):
@@ -83,6 +108,27 @@ def main():
         assert hf < 2e-5, (name, hf)
         np.savez_compressed(os.path.join(HERE, name + ".npz"), out=out.numpy(), k_new=kn.numpy(), v_new=vn.numpy(),
                             in_checksum=checksum(x, w["qkv_weight"], w["mlp_down_weight"], k, v), hf_maxdiff=np.array(hf))
+        print(name, "hf maxdiff", hf)
+    for name, seq, seed in LLAMA_ATTN_CASES:
+        t = llama_attn_inputs(seq, seed)
+        args = (t["x"], t["res"], t["wqkv"], t["wo"], t["k"], t["v"], t["g"], LLAMA_EPS, t["cos"], t["sin"])
+        out, res, kn, vn = L.llama_attn_block_fp32(*args)
+        ho, hr, hk, hv = L.hf_llama_attn_block(*args)
+        hf = max(O.compare(out, ho)[0], O.compare(kn, hk)[0], O.compare(vn, hv)[0])
+        assert hf < 2e-5 and torch.equal(res, hr), (name, hf)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), out=out.numpy(), residual=res.numpy(), k_new=kn.numpy(),
+                            v_new=vn.numpy(), in_checksum=checksum(t["x"], t["wqkv"], t["wo"], t["k"], t["v"]),
+                            hf_maxdiff=np.array(hf))
+        print(name, "hf maxdiff", hf)
+    for name, ffn, seed in LLAMA_MLP_CASES:
+        t = llama_mlp_inputs(ffn, seed)
+        args = (t["x"], t["res"], t["wgu"], t["wd"], t["g"], LLAMA_EPS)
+        out, res = L.llama_mlp_block_fp32(*args)
+        ho, hr = L.hf_llama_mlp_block(*args)
+        hf = O.compare(out, ho)[0]
+        assert hf < 2e-5 and torch.equal(res, hr), (name, hf)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), out=out.numpy(), residual=res.numpy(),
+                            in_checksum=checksum(t["x"], t["wgu"], t["wd"]), hf_maxdiff=np.array(hf))
         print(name, "hf maxdiff", hf)
     prompt, tokens, gaps, logits = mini_rollout_oracle(round_io=False)
     np.savez_compressed(os.path.join(HERE, "mini_rollout.npz"), prompt=np.array(prompt), tokens=np.array(tokens),

@@ -13,6 +13,9 @@ from _util import REL_L2, assert_close  # noqa: E402
 from oracle import llama_oracle as L  # noqa: E402
 from oracle import pythia_oracle as O  # noqa: E402
 
+sys.path.insert(0, os.path.join(HERE, "golden"))
+import make_golden as G  # noqa: E402
+
 pytestmark = pytest.mark.gpu
 H, NH, D = 4096, 32, 128
 
@@ -128,3 +131,24 @@ def test_llama_layer_stack_class_matches_block_calls(cuda_device):
         x, res = cf.llama_mlp_sglang(x, res, m["wgu"], m["wd"], m["g"], 1e-5)
     assert torch.equal(x, xs) and torch.equal(res, rs)
     assert cf.device_status() == 0
+
+
+@pytest.mark.parametrize("case", G.LLAMA_ATTN_CASES + G.LLAMA_MLP_CASES, ids=lambda c: c[0])
+def test_llama_blocks_vs_golden_fixture(cuda_device, case):
+    """The kernels against the committed fixtures: inputs regenerated from the seed on the CPU, moved to the GPU."""
+    import numpy as np
+    import clusterfusion as cf
+    name, size, seed = case
+    gold = np.load(os.path.join(HERE, "golden", name + ".npz"))
+    if name.startswith("llama_attn"):
+        t = {k: v.to(cuda_device) for k, v in G.llama_attn_inputs(size, seed).items()}
+        out, res, kn, vn = cf.llama_decoder_layer_sglang(t["x"], t["res"], t["wqkv"], t["wo"], t["k"], t["v"], t["g"],
+                                                         G.LLAMA_EPS, t["cos"], t["sin"])
+        assert_close(kn, torch.from_numpy(gold["k_new"]), "k_new")
+        assert_close(vn, torch.from_numpy(gold["v_new"]), "v_new")
+    else:
+        t = {k: v.to(cuda_device) for k, v in G.llama_mlp_inputs(size, seed).items()}
+        out, res = cf.llama_mlp_sglang(t["x"], t["res"], t["wgu"], t["wd"], t["g"], G.LLAMA_EPS)
+    assert cf.device_status() == 0
+    assert torch.equal(res.float().cpu(), torch.from_numpy(gold["residual"]))
+    assert_close(out, torch.from_numpy(gold["out"]), "output")

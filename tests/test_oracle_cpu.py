@@ -119,3 +119,26 @@ def test_llama_mlp_oracle_matches_hf_mlp():
     b = L.hf_llama_mlp_block(x, r, wgu, wd, gm, 1e-6)
     assert torch.equal(a[1], b[1])
     assert torch.allclose(a[0], b[0], atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("case", G.LLAMA_ATTN_CASES + G.LLAMA_MLP_CASES, ids=lambda c: c[0])
+def test_llama_oracle_reproduces_golden(case):
+    """The Llama restatements against the committed fixtures (made by tests/golden/make_golden.py, where
+    they were also cross-checked against transformers' LlamaAttention / LlamaMLP)."""
+    from oracle import llama_oracle as L
+    name, size, seed = case
+    gold = np.load(os.path.join(HERE, "golden", name + ".npz"))
+    assert float(gold["hf_maxdiff"]) < 2e-5
+    if name.startswith("llama_attn"):
+        t = G.llama_attn_inputs(size, seed)
+        np.testing.assert_allclose(G.checksum(t["x"], t["wqkv"], t["wo"], t["k"], t["v"]), gold["in_checksum"], rtol=1e-9)
+        out, res, kn, vn = L.llama_attn_block_fp32(t["x"], t["res"], t["wqkv"], t["wo"], t["k"], t["v"], t["g"],
+                                                   G.LLAMA_EPS, t["cos"], t["sin"])
+        np.testing.assert_allclose(kn.numpy(), gold["k_new"], atol=1e-5, rtol=1e-5)
+        np.testing.assert_allclose(vn.numpy(), gold["v_new"], atol=1e-5, rtol=1e-5)
+    else:
+        t = G.llama_mlp_inputs(size, seed)
+        np.testing.assert_allclose(G.checksum(t["x"], t["wgu"], t["wd"]), gold["in_checksum"], rtol=1e-9)
+        out, res = L.llama_mlp_block_fp32(t["x"], t["res"], t["wgu"], t["wd"], t["g"], G.LLAMA_EPS)
+    np.testing.assert_array_equal(res.numpy(), gold["residual"])
+    np.testing.assert_allclose(out.numpy(), gold["out"], atol=1e-5, rtol=1e-5)
