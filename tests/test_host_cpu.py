@@ -29,6 +29,29 @@ def test_library_exports_every_declared_symbol():
     assert sorted(_lib.SIGNATURES) == syms
 
 
+def test_header_is_plain_c_and_links_against_the_library(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 and as C++11 without torch or CUDA headers,
+    and a C program linked against the shared library resolves and calls an entry point."""
+    import shutil
+    import subprocess
+    from clusterfusionplus_b200 import _lib
+    if not shutil.which("gcc") or not shutil.which("g++"):
+        pytest.skip("no host compiler")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include <stdio.h>\n#include "clusterfusion_b200.h"\n'
+                   'int main(void) { CfDims d; int rc = cf_model_dims(CF_PYTHIA_6B9, &d);\n'
+                   '  printf("%d %d %d %d\\n", rc, d.hidden, d.heads, d.head_dim); return rc; }\n')
+    inc = os.path.join(ROOT, "include")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I", inc, str(src)], check=True)
+    subprocess.run(["g++", "-std=c++11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", "-I", inc, str(src)], check=True)
+    exe = tmp_path / "use_header"
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run(["gcc", "-std=c99", "-I", inc, str(src), "-o", str(exe), "-L", libdir, "-lclusterfusion_b200",
+                    f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out == ["0", "4096", "32", "128"]
+
+
 def test_error_string_without_gpu():
     """No CPU fallback: on a box without a CUDA device the entry points fail and say why."""
     from clusterfusionplus_b200 import _lib
