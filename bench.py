@@ -40,10 +40,10 @@ SHAPES = {  # hidden, heads, head_dim, rotary, ffn, vocab
     "2b8": (2560, 32, 80, 20, 10240, 50304),
 }
 
-# DRAM traffic of ONE whole-token launch (6.9B, 4096 cached rows), from ncu captures of 2- and
-# 4-layer models of the same shapes scaled to 32 layers (dram__bytes_read.sum +
-# dram__bytes_write.sum).
-NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = 15.551e9  # 417.9 MB tail + 32 x 472.9 MB (profiles/decoder_6b9_ctx4096_traffic.md)
+# DRAM traffic of ONE whole-token launch (6.9B, 4096 cached rows): dram__bytes_read.sum +
+# dram__bytes_write.sum of ncu captures of 2- and 4-layer models of the same shapes, scaled to 32
+# layers (traffic is linear in the layer count): 417.9 MB for the tail + 32 x 472.9 MB per layer.
+NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = 15.551e9
 
 
 def algorithmic_bytes_per_token(model: str, n_layers: int, ctx: float, tp: int = 1) -> float:
@@ -156,40 +156,126 @@ def workload_config(args, tp):
             "l2": "inputs larger than L2 (weights + KV read once per token: GBs vs 126 MB)"}
 
 
+def read_ceiling_gbs(dev, hidden, reps=10):
+    """Read bandwidth the decode kernel's own streaming machinery reaches when nothing waits on other
+    CTAs: one launch streams a [393216, hidden] fp16 matrix (3.2 GB at hidden 4096, far larger than L2)
+    through the same persistent grid, TMA ring and row-GEMV consumers as the LM-head phase
+    (cf_debug_stream_rows).  Returns (with the dot products, consumers only touching the stages)."""
+    import ctypes as C
+    from clusterfusionplus_b200 import _lib
+    rows = 393216
+    m = torch.empty(rows, hidden, dtype=torch.float16, device=dev).normal_(0, 0.02)
+    x = torch.randn(hidden, device=dev).half()
+    desc = torch.zeros(1024, dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    out = []
+    for touch in (0, 1):
+        def call():
+            _lib.check(_lib.lib.cf_debug_stream_rows(m.data_ptr(), rows, hidden, x.data_ptr(), touch, desc.data_ptr(), st))
+        for _ in range(3):
+            call()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = None
+        for _ in range(reps):
+            torch.cuda.synchronize()
+            e0.record()
+            call()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        out.append(rows * hidden * 2 / (best * 1e-3) / 1e9)
+    del m
+    return out[0], out[1]
+
+
 # ------------------------------------------------------------------------------------ GPU arm
 def rand_half(shape, gen, dev, mean=0.0, std=0.02):
     return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std + mean).half()
 
 
-def build_model(args, dev, rank, tp):
-    """Seeded random-init tensors straight on the GPU.  Replicated tensors use the same seed on
-    every rank, sharded ones a rank-specific seed (any N(0, 0.02) shard is as good as another)."""
+PARITY_STEPS = 16       # greedy tokens compared between the tensor-parallel and the single-GPU decoder
+NEAR_TIE_GAP = 5e-3     # a token mismatch only counts as a near tie below this top-2 logit gap (logit std ~ 1.3)
+
+
+def build_model(args, dev):
+    """ONE seeded random-init model, unsharded, straight on the GPU.  Every rank draws the same
+    tensors from the same seed (same generator, same GPU type), so the ranks' shards are slices
+    of one model and the tensor-parallel result can be compared with a single-GPU decode of it."""
     H, NH, D, R, F, V = SHAPES[args.model]
-    g_rep = torch.Generator(device=dev)
-    g_rep.manual_seed(1234)
-    g_loc = torch.Generator(device=dev)
-    g_loc.manual_seed(999 + rank)
-    nh, f, v = NH // tp, F // tp, V // tp
-    kvw = nh * D
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    kvw = NH * D
     layers, caches = [], []
-    max_seq = args.ctx + args.steps + args.warmup + 2 * 8 + 8
+    max_seq = args.ctx + max(args.steps + args.warmup, PARITY_STEPS) + 2 * 8 + 8
     for _ in range(args.layers):
         layers.append({
-            "qkv_weight": rand_half((3 * kvw, H), g_loc, dev), "qkv_bias": rand_half((3 * kvw,), g_loc, dev),
-            "o_weight": rand_half((H, kvw), g_loc, dev), "o_bias": rand_half((H,), g_rep, dev),
-            "ln_weight": rand_half((H,), g_rep, dev, 1.0), "ln_bias": rand_half((H,), g_rep, dev),
-            "post_ln_weight": rand_half((H,), g_rep, dev, 1.0), "post_ln_bias": rand_half((H,), g_rep, dev),
-            "mlp_up_weight": rand_half((f, H), g_loc, dev), "mlp_up_bias": rand_half((f,), g_loc, dev),
-            "mlp_down_weight": rand_half((H, f), g_loc, dev), "mlp_down_bias": rand_half((H,), g_rep, dev),
+            "qkv_weight": rand_half((3 * kvw, H), g, dev), "qkv_bias": rand_half((3 * kvw,), g, dev),
+            "o_weight": rand_half((H, kvw), g, dev), "o_bias": rand_half((H,), g, dev),
+            "ln_weight": rand_half((H,), g, dev, 1.0), "ln_bias": rand_half((H,), g, dev),
+            "post_ln_weight": rand_half((H,), g, dev, 1.0), "post_ln_bias": rand_half((H,), g, dev),
+            "mlp_up_weight": rand_half((F, H), g, dev), "mlp_up_bias": rand_half((F,), g, dev),
+            "mlp_down_weight": rand_half((H, F), g, dev), "mlp_down_bias": rand_half((H,), g, dev),
         })
         k = torch.zeros(max_seq, kvw, dtype=torch.float16, device=dev)
         vv = torch.zeros(max_seq, kvw, dtype=torch.float16, device=dev)
-        k[:args.ctx] = rand_half((args.ctx, kvw), g_loc, dev, std=1.0)
-        vv[:args.ctx] = rand_half((args.ctx, kvw), g_loc, dev, std=1.0)
+        k[:args.ctx] = rand_half((args.ctx, kvw), g, dev, std=1.0)
+        vv[:args.ctx] = rand_half((args.ctx, kvw), g, dev, std=1.0)
         caches.append((k, vv))
-    head = {"embed_in": rand_half((V, H), g_rep, dev), "final_ln_weight": rand_half((H,), g_rep, dev, 1.0),
-            "final_ln_bias": rand_half((H,), g_rep, dev), "embed_out": rand_half((v, H), g_loc, dev)}
+    head = {"embed_in": rand_half((V, H), g, dev), "final_ln_weight": rand_half((H,), g, dev, 1.0),
+            "final_ln_bias": rand_half((H,), g, dev), "embed_out": rand_half((V, H), g, dev)}
     return layers, head, caches, max_seq
+
+
+def shard_model(cf, dims, layers, head, caches, rank, tp):
+    """This rank's contiguous shards of the one model (heads / MLP columns / vocabulary rows)."""
+    loc_layers = [cf.shard_layer_weights(w, dims, rank, tp) for w in layers]
+    loc_head = cf.shard_head_weights(head, dims, rank, tp)
+    loc_caches = [(cf.shard_cache(k, dims, rank, tp), cf.shard_cache(v, dims, rank, tp)) for k, v in caches]
+    return loc_layers, loc_head, loc_caches
+
+
+def tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp, dev):
+    """Outside every timed region: PARITY_STEPS greedy tokens from the tensor-parallel decoder; all
+    ranks must agree on them; rank 0 then decodes the same steps on ONE GPU over the unsharded
+    tensors and compares tokens (a mismatch at a step whose top-2 logit gap is below NEAR_TIE_GAP
+    is reported as a near tie: the two decoders add the partial sums in different orders) and the
+    first step's hidden state (max-abs 2e-2, relative L2 1e-3)."""
+    dec.reset(args.ctx, 17)
+    toks, hid0 = [], None
+    for i in range(PARITY_STEPS):
+        dec.step()
+        toks.append(int(dec.token.item()))
+        if i == 0:
+            hid0 = dec.hidden.clone()
+    status = cf.device_status()
+    gathered = [None] * tp
+    dist.all_gather_object(gathered, (toks, int(status)))
+    out = {"steps": PARITY_STEPS, "ranks_agree": all(g[0] == gathered[0][0] for g in gathered),
+           "device_status": max(g[1] for g in gathered)}
+    if rank == 0:
+        ref_caches = [(k.clone(), v.clone()) for k, v in caches]
+        ref = cf.PythiaDecoder(dims, layers, head, ref_caches, max_seq, use_graph=False)
+        ref.reset(args.ctx, 17)
+        ref_toks, gaps, herr = [], [], None
+        for i in range(PARITY_STEPS):
+            ref.step()
+            ref_toks.append(int(ref.token.item()))
+            top2 = torch.topk(ref.logits, 2).values
+            gaps.append(float(top2[0] - top2[1]))
+            if i == 0:
+                d = (hid0.float() - ref.hidden.float()).reshape(-1)
+                herr = (float(d.abs().max()), float(d.norm() / ref.hidden.float().norm()))
+        out["device_status"] = max(out["device_status"], int(cf.device_status()))
+        ref.close()
+        first = next((i for i, (a, b) in enumerate(zip(toks, ref_toks)) if a != b), None)
+        near_tie = first is not None and gaps[first] < NEAR_TIE_GAP
+        out.update({"equals_single_gpu": first is None or near_tie, "first_mismatch": first,
+                    "mismatch_is_near_tie": near_tie if first is not None else None,
+                    "min_top2_gap": min(gaps), "hidden_max_abs": herr[0], "hidden_rel_l2": herr[1],
+                    "hidden_within_tolerance": herr[0] <= 2e-2 and herr[1] <= 1e-3})
+    dist.barrier()
+    return out
 
 
 def run_ours(args, rank, world):
@@ -205,12 +291,16 @@ def run_ours(args, rank, world):
     H, NH, D, R, F, V = SHAPES[args.model]
     dims = cf.CfDims()
     dims.hidden, dims.heads, dims.head_dim, dims.rotary, dims.ffn, dims.vocab = H, NH, D, R, F, V
-    layers, head, caches, max_seq = build_model(args, dev, rank, tp)
+    layers, head, caches, max_seq = build_model(args, dev)
     if tp == 1:
         dec = cf.PythiaDecoder(dims, layers, head, caches, max_seq, use_graph=True)
         launches_per_token = 1
     else:
-        dec = cf.TPDecoder(dims, layers, head, caches, max_seq, use_graph=True, fused=(args.tp_mode == "fused"))
+        loc_layers, loc_head, loc_caches = shard_model(cf, dims, layers, head, caches, rank, tp)
+        if rank != 0:   # only rank 0 keeps the unsharded tensors (for the single-GPU comparison)
+            layers = head = caches = None
+            torch.cuda.empty_cache()
+        dec = cf.TPDecoder(dims, loc_layers, loc_head, loc_caches, max_seq, use_graph=True, fused=(args.tp_mode == "fused"))
         launches_per_token = dec.launches_per_token
     K, W = args.steps, args.warmup
 
@@ -274,6 +364,9 @@ def run_ours(args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = t.item()
     status = status or cf.device_status()
+    parity = None
+    if tp > 1 and not args.no_parity:
+        parity = tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp, dev)
     if rank != 0:
         dec.close()
         if tp > 1:
@@ -287,10 +380,16 @@ def run_ours(args, rank, world):
     if tp == 1 and args.model == "6b9" and args.ctx == 4096 and args.layers == 32:
         traffic = NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K
     metric = METRIC if (args.model == "6b9" and args.ctx == 4096) else f"Pythia-{args.model} B=1 decode TPOT (us) at {args.ctx} context"
+    config = workload_config(args, tp)
+    parity_ok = True
+    if parity is not None:
+        config["parity"] = parity
+        parity_ok = (parity["ranks_agree"] and parity["equals_single_gpu"] and parity["hidden_within_tolerance"]
+                     and parity["device_status"] == 0)
     line = {
         "metric": metric, "value": tpot_us, "unit": "us/token", "n_gpus": tp, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-        "dtype": "fp16 (fp32 accumulate)", "data": "synthetic", "config": workload_config(args, tp),
+        "dtype": "fp16 (fp32 accumulate)", "data": "synthetic", "config": config,
         "clocks": clocks,
         "e2e": {"value": e2e_ms / K * 1e3, "unit": "us/token", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
         "gpu_launches": K * launches_per_token,
@@ -302,6 +401,14 @@ def run_ours(args, rank, world):
         "launch": cf.launch_info(cf.CF_PYTHIA_6B9 if args.model == "6b9" else cf.CF_PYTHIA_2B8),
         "device_status": status,
     }
+    if tp == 1 and not args.no_read_ceiling:
+        with_math, touch = read_ceiling_gbs(dev, H)
+        line["roofline"]["read_ceiling_gbs"] = with_math
+        line["roofline"]["read_ceiling_touch_only_gbs"] = touch
+        line["roofline"]["frac_of_read_ceiling"] = achieved / with_math
+        line["roofline"]["read_ceiling_how"] = ("one launch of the same persistent grid, TMA ring and row-GEMV consumers "
+                                                "streaming a 3.2 GB fp16 matrix with no cross-CTA waits; best of 10")
+        line["device_status"] = line["device_status"] or cf.device_status()
     if tp == 1 and not args.no_cpu_baseline:
         times, cores = oracle_tpot_us(args.model, args.layers, args.ctx, args.sample_layers, 5, 1)
         line["cpu_baseline"] = {
@@ -312,6 +419,8 @@ def run_ours(args, rank, world):
     dec.close()
     if tp > 1:
         dist.destroy_process_group()
+    if not parity_ok:
+        raise SystemExit(f"tensor-parallel parity check failed: {json.dumps(parity)}")
 
 
 def tensor_peak():
@@ -337,7 +446,7 @@ def run_prefill(args):
     m = args.prefill_tokens
     H, NH, D, R, F, V = SHAPES[args.model]
     args.ctx = 0
-    layers, head, caches, _ = build_model(args, dev, 0, 1)
+    layers, head, caches, _ = build_model(args, dev)
     max_seq = caches[0][0].shape[0]
     if m + 1 > max_seq:
         caches = [(torch.zeros(m + 8, NH * D, dtype=torch.float16, device=dev),
@@ -461,6 +570,10 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--sample-layers", type=int, default=2, help="layers the CPU oracle runs per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-read-ceiling", action="store_true",
+                    help="skip the measurement of the kernel's own read-streaming ceiling (N = 1)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="N > 1: skip the comparison with a single-GPU decode of the same model (outside the timed regions)")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N > 1: in-kernel all-reduce over peer memory (default) or one NCCL all-reduce per layer")
     ap.add_argument("--llama-ctx", type=int, default=0,

@@ -68,6 +68,7 @@ SIGNATURES = {
     "cf_llama_mlp_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_debug_run_phases": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_int, C.c_void_p]),
     "cf_debug_set_trace": (C.c_int, [C.c_void_p, C.c_int64]),
+    "cf_debug_stream_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "cf_pythia_attention_only": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
     "cf_pythia_mlp_only": (C.c_int, [C.c_int] + [C.c_void_p] * 7),
     "cf_pythia_create_graph_context": (C.c_int, [C.c_int, C.c_int64] + [C.c_void_p] * 6 + [C.c_int64]),
@@ -90,6 +91,8 @@ SIGNATURES = {
     "cf_decoder_tail": (C.c_int, [C.c_int64, C.c_void_p]),
     "cf_decoder_select_token": (C.c_int, [C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_decoder_destroy": (C.c_int, [C.c_int64]),
+    "cf_decoder_status": (C.c_int, [C.c_int64, _P(C.c_int)]),
+    "cf_debug_noalloc_scratch": (C.c_int, [_P(C.c_void_p), _P(C.c_int64), _P(C.c_int64)]),
     "cf_prefill_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                     C.c_int64, C.c_int, C.c_void_p]),
 }

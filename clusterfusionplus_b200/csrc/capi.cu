@@ -47,6 +47,22 @@ int fail(int code, const char* fmt, ...) {
         if (e_ != cudaSuccess) return fail(CF_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
+// A descriptor upload copies from host memory that does not outlive the call.  Recorded into a
+// stream capture, the copy node would keep that pointer and read it again at every replay, so an
+// upload is refused while the stream is capturing: the caller makes the call once outside the
+// capture (which caches the descriptor) and captures afterwards.
+int refuse_upload_in_capture(cudaStream_t st, const char* what) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(st, &cs);
+    if (e != cudaSuccess) return fail(CF_ERR_CUDA, "cudaStreamIsCapturing failed: %s", cudaGetErrorString(e));
+    if (cs != cudaStreamCaptureStatusNone)
+        return fail(CF_ERR_INVALID,
+                    "%s: these tensors need a descriptor upload, which cannot be recorded into a stream capture; "
+                    "call once with the same tensors outside the capture first",
+                    what);
+    return CF_OK;
+}
+
 const CfDims kDims[2] = {
     {2560, 32, 80, 20, 10240, 50304},
     {4096, 32, 128, 32, 16384, 50432},
@@ -415,7 +431,7 @@ void base_params(Params& p, const CfDims& d, const Workspace& ws) {
     p.R = d.rotary;
     p.F = d.ffn;
     p.qkv_ll = ws.qkv_ll;
-    p.launch_count = ws.sync + 2;
+    p.epoch_base = ws.sync + 2;
     p.hid_ll[0] = ws.hid_ll[0];
     p.hid_ll[1] = ws.hid_ll[1];
     p.mid_f32 = ws.mid_f32;
@@ -474,6 +490,10 @@ int cached_desc(DeviceState& ds, const CfDims& d, const CfLayerWeights& w, void*
     if (it != ds.desc_cache.end()) {
         *out = it->second;
         return CF_OK;
+    }
+    {
+        int rc = refuse_upload_in_capture(st, "layer call");
+        if (rc != CF_OK) return rc;
     }
     if (ds.desc_cache.size() >= 1024) {  // callers that churn tensors: start over
         // entries may still be referenced by launches in flight
@@ -745,8 +765,19 @@ int cf_get_status(int* status) {
         for (auto& kv : g_decoders)
             if (kv.second->dev == ds->dev && (rc = probe(kv.second->ws))) return rc;
     }
+    {
+        // the static scratch of the allocation-free entry point, once a call has set it up on this device
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (ds->dev >= 0 && ds->dev < NOALLOC_MAX_DEVICES && g_noalloc[ds->dev].ready &&
+            (rc = probe(g_noalloc[ds->dev].ds.ws)))
+            return rc;
+    }
     *status = worst;
-    if (worst != 0) return fail(CF_ERR_DEVICE, "device status %d (1-2 TMA ring, 3 grid barrier, 4 cluster exchange, 5 bad seq_len, 6 drain)", worst);
+    if (worst != 0)
+        return fail(CF_ERR_DEVICE,
+                    "device status %d (1-2 TMA ring, 3 grid barrier / flag wait, 4 cluster exchange, 5 bad seq_len, "
+                    "6 drain, 7 tensor-parallel peer never answered)",
+                    worst);
     return CF_OK;
 }
 
@@ -777,10 +808,6 @@ int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const Cf
         return fail(CF_ERR_UNSUPPORTED, "this GPU runs %d CTAs; the static scratch holds partials for at most %d",
                     nd->ds.cfg[d.head_dim == 128].grid, NOALLOC_MAX_GRID);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // the array keeps whatever the last call left: barrier and status words must start at zero
-    // (the third sync word is the launch count behind the q/k/v epochs: it must keep counting)
-    CF_CUDA(cudaMemsetAsync(nd->ds.ws.sync, 0, 8, st));
-    CF_CUDA(cudaMemsetAsync(nd->ds.ws.status, 0, 4, st));
     // tensor maps + pointers of this call's tensors into the descriptor slot (a copy, not an allocation)
     DescKey key;
     memset(&key, 0, sizeof(key));
@@ -791,7 +818,14 @@ int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const Cf
     key.kv_rows = io->kv_rows;
     key.dims[0] = d.hidden; key.dims[1] = d.heads; key.dims[2] = d.head_dim; key.dims[3] = d.ffn; key.dims[4] = d.rotary;
     LayerDesc* desc = reinterpret_cast<LayerDesc*>(nd->scratch + NA_OFF_DESC);
-    if (!nd->have_key || memcmp(&key, &nd->last_key, sizeof(key)) != 0) {
+    const bool upload = !nd->have_key || memcmp(&key, &nd->last_key, sizeof(key)) != 0;
+    if (upload && (rc = refuse_upload_in_capture(st, "noalloc layer call"))) return rc;
+    // The array keeps whatever the last call left: the two barrier words must start at zero.  The
+    // third sync word is the running base of the q/k/v epochs and keeps counting; the status word is
+    // left alone so that a failure of an earlier launch stays readable until cf_get_status reports
+    // (and clears) it.
+    CF_CUDA(cudaMemsetAsync(nd->ds.ws.sync, 0, 8, st));
+    if (upload) {
         LayerDesc host;
         if ((rc = build_layer_desc(host, d, *w, io->k_cache, io->v_cache, io->kv_rows))) return rc;
         CF_CUDA(cudaMemcpyAsync(desc, &host, sizeof(LayerDesc), cudaMemcpyHostToDevice, st));
@@ -917,6 +951,37 @@ int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io,
     p.cos = io->cos;
     p.sin = io->sin;
     p.seq_host = static_cast<int>(seq_len);
+    return launch(*ds, d, p, st);
+}
+
+int cf_debug_stream_rows(const void* matrix, int64_t rows, int64_t cols, const void* x, int touch_only,
+                         void* scratch_desc, void* stream) {
+    if (!matrix || !x || !scratch_desc) return fail(CF_ERR_INVALID, "null pointer");
+    if (rows <= 0 || rows > 0x7fffffff || (rows % GRAN) != 0) return fail(CF_ERR_INVALID, "rows %lld", (long long)rows);
+    if (cols <= 0 || cols > MAX_H || (cols % KCHUNK) != 0) return fail(CF_ERR_INVALID, "cols %lld", (long long)cols);
+    if (reinterpret_cast<uintptr_t>(scratch_desc) & 127) return fail(CF_ERR_INVALID, "scratch_desc must be 128-byte aligned");
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if ((rc = refuse_upload_in_capture(st, "cf_debug_stream_rows"))) return rc;
+    TailDesc host;
+    memset(&host, 0, sizeof(host));
+    if ((rc = encode_weight(&host.tm_head, matrix, static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)))) return rc;
+    // LayerNorm parameters of the tail: the activation vector itself serves (only the stream is timed)
+    host.fln_w = static_cast<const __half*>(x);
+    host.fln_b = static_cast<const __half*>(x);
+    host.vocab = static_cast<int>(rows);
+    CF_CUDA(cudaMemcpyAsync(scratch_desc, &host, sizeof(TailDesc), cudaMemcpyHostToDevice, st));
+    CF_CUDA(cudaStreamSynchronize(st));  // `host` leaves scope
+    const CfDims d = {static_cast<int>(cols), 32, 128, 0, 0, static_cast<int>(rows)};  // heads: launch-geometry checks only
+    Params p;
+    base_params(p, d, ds->ws);
+    p.tail = static_cast<const TailDesc*>(scratch_desc);
+    p.n_layers = 0;
+    p.phase_mask = PH_P4;
+    p.x_in = static_cast<const __half*>(x);
+    p.touch_only = touch_only ? 1 : 0;
     return launch(*ds, d, p, st);
 }
 
@@ -1094,6 +1159,7 @@ int cf_pythia_graph_decode_step(int model, int64_t context_id, const CfStepArgs*
         }
     if (ctx->dirty) {
         // first step of a context (or new small tensors): not capturable, like any upload
+        if ((rc = refuse_upload_in_capture(st, "graph_decode_step"))) return rc;
         CF_CUDA(cudaMemcpyAsync(ctx->dev, &ctx->host, sizeof(LayerDesc), cudaMemcpyHostToDevice, st));
         ctx->dirty = false;
     }
@@ -1347,7 +1413,7 @@ int cf_decoder_step(int64_t handle, void* stream) {
         p.tp_size = dc->cfg.tp_size;
         p.tp_rank = dc->cfg.tp_rank;
         for (int r = 0; r < dc->cfg.tp_size; ++r) p.tp_peer[r] = dc->tp_peer[r];
-        p.tp_launch_count = dc->tp_count;
+        p.tp_epoch_base = dc->tp_count;
     }
     p.layers = dc->layers_d;
     p.tail = dc->tail_d;
@@ -1430,6 +1496,28 @@ int cf_decoder_select_token(int64_t handle, const float* pairs_val, const int* p
     select_token_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pairs_val, pairs_idx, dc->cfg.tp_size,
                                                                         dc->token_d, dc->seq_d);
     CF_CUDA(cudaGetLastError());
+    return CF_OK;
+}
+
+int cf_decoder_status(int64_t handle, int* status) {
+    Decoder* dc;
+    int rc = find_decoder(handle, &dc);
+    if (rc) return rc;
+    if (!status) return fail(CF_ERR_INVALID, "null status");
+    // a blocking 4-byte read: it waits for the work queued before it on the legacy default stream
+    // (and the streams that synchronise with it); callers on other streams synchronise first
+    CF_CUDA(cudaMemcpy(status, dc->ws.status, sizeof(int), cudaMemcpyDeviceToHost));
+    return CF_OK;
+}
+
+int cf_debug_noalloc_scratch(void** base, int64_t* bytes, int64_t* status_offset) {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocDevice* nd;
+    int rc = noalloc_setup(&nd);
+    if (rc) return rc;
+    if (base) *base = nd->scratch;
+    if (bytes) *bytes = static_cast<int64_t>(NOALLOC_SCRATCH_BYTES);
+    if (status_offset) *status_offset = static_cast<int64_t>(NA_OFF_SYNC + 16);
     return CF_OK;
 }
 

@@ -137,13 +137,13 @@ struct Params {
     const __half* extra_add_f16;  // optional [H] added in the P3 epilogue
     // scratch
     uint2* qkv_ll;     // [3*NH*D] {fp32 bits, epoch}: q/k/v rows travel with the epoch of their launch and layer
-    unsigned* launch_count;  // +1 per launch (last CTA out): makes those epochs unique
+    unsigned* epoch_base;    // running base of those epochs; the last CTA out adds (layers + 2)
     int qkv_any_epoch; // the launch has no P1: take whatever an earlier launch left in qkv_ll
     float* mid_f32;    // [F]
     float* attn_part;  // [grid][MAXL][D+4]: D numerators, max, denominator, epoch (written last), 1 pad
     float* attn_new;   // [NH][D+4], same record
     int part_any_epoch;  // the launch has no P2: take the attention partials an earlier launch left
-    unsigned* sync;    // [0] barrier count, [1] exit count, [2] launch count, [3] CTAs past P1 (counts up over layers)
+    unsigned* sync;    // [0] barrier count, [1] exit count, [2] epoch base, [3] CTAs past P1 (counts up over layers)
     int* status;
     // tail outputs
     float* logits;     // optional [vocab]
@@ -162,17 +162,18 @@ struct Params {
     __half* residual_out;       // [H], AF_RMS_ADD: x + residual (must not alias residual_in)
     // optional timeline: [grid][n_layers + 1][TRACE_EVENTS] globaltimer stamps (diagnostics)
     unsigned long long* trace;
+    int touch_only;    // diagnostics: row-GEMV consumers take and release the stages without the arithmetic
     // tensor-parallel exchange over peer memory (tp_size > 1): every rank owns one buffer laid
     // out as TpLayout; tp_peer[r] is rank r's buffer as mapped into this process.
     int tp_size, tp_rank;
     unsigned char* tp_peer[MAX_TP];
-    unsigned* tp_launch_count;  // local word, +1 per launch: makes epochs strictly increasing
+    unsigned* tp_epoch_base;    // two local words: [0] running epoch base of the exchanges, [1] launches so far
 };
 
 // Exchange buffer of one rank (H = hidden).  Every word travels with the epoch it belongs
 // to in the same aligned 8-byte store (value, epoch), so a reader that sees the epoch has the
 // value: no fence and no separate flag, one NVLink crossing of latency.
-//   partial[2][tp][H]  {fp32 value, u32 epoch}   slot [layer parity][source rank]
+//   partial[2][tp][H]  {fp32 value, u32 epoch}   slot [epoch parity][source rank]
 //   pairs  [2][tp][2]  {bits, u32 epoch}         slot [launch parity][source rank]: max logit, index
 struct TpLayout {
     int H, tp;
@@ -184,24 +185,48 @@ struct TpLayout {
 // pause between re-reads of a word in global memory that has not arrived yet
 constexpr int POLL_BACKOFF_NS = 96;
 
+// A tagged word is ONE naturally aligned 64-bit access, {payload bits (low), epoch (high)}: the
+// PTX memory model makes an aligned scalar b64 single-copy atomic, so a reader that sees the epoch
+// has the payload that was stored with it (a v2.u32 access would formally be two accesses).
+// Scope: .gpu for words that stay on this GPU, .sys for words a peer GPU writes or reads.
+__device__ __forceinline__ unsigned long long ll_pack(unsigned bits, unsigned epoch) {
+    return (static_cast<unsigned long long>(epoch) << 32) | bits;
+}
+__device__ __forceinline__ uint2 ll_unpack(unsigned long long v) {
+    return make_uint2(static_cast<unsigned>(v), static_cast<unsigned>(v >> 32));
+}
 __device__ __forceinline__ void st_ll(void* p, unsigned bits, unsigned epoch) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(bits), "r"(epoch) : "memory");
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(ll_pack(bits, epoch)) : "memory");
+}
+__device__ __forceinline__ void st_ll_sys(void* p, unsigned bits, unsigned epoch) {
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(ll_pack(bits, epoch)) : "memory");
 }
 __device__ __forceinline__ uint2 ld_ll(const void* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return ll_unpack(v);
 }
-// two adjacent words in one 16-byte load: {bits0, epoch0, bits1, epoch1}
+__device__ __forceinline__ uint2 ld_ll_sys(const void* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return ll_unpack(v);
+}
+// two adjacent words in one 16-byte load (each b64 element is atomic on its own): {bits0, epoch0, bits1, epoch1}
 __device__ __forceinline__ uint4 ld_ll2(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4(static_cast<unsigned>(a), static_cast<unsigned>(a >> 32), static_cast<unsigned>(b),
+                      static_cast<unsigned>(b >> 32));
 }
 // wait (bounded) until the word at p carries `epoch`; returns its payload bits
 __device__ __forceinline__ unsigned wait_ll(const void* p, unsigned epoch, const AbortCtl& ab) {
     uint2 v = ld_ll(p);
     if (v.y != epoch) wait_bounded<POLL_BACKOFF_NS>([&] { v = ld_ll(p); return v.y == epoch; }, ab, ST_TIMEOUT_PEER);
+    return v.x;
+}
+__device__ __forceinline__ unsigned wait_ll_sys(const void* p, unsigned epoch, const AbortCtl& ab) {
+    uint2 v = ld_ll_sys(p);
+    if (v.y != epoch) wait_bounded<POLL_BACKOFF_NS>([&] { v = ld_ll_sys(p); return v.y == epoch; }, ab, ST_TIMEOUT_PEER);
     return v.x;
 }
 
@@ -775,6 +800,7 @@ struct Consumer {
     Cursor cur;
     AbortCtl ab;
     int warp, lane;
+    bool touch_only;
 
     __device__ __forceinline__ const uint8_t* wait_stage() {
         mbar_wait(full_addr + cur.stage * 8, cur.phase, ab, ST_TIMEOUT_FULL);
@@ -804,8 +830,10 @@ struct Consumer {
             for (int c = 0; c < KC; ++c) {
                 if (c == gate_chunk && r == 0) mbar_wait(gate_bar, gate_parity, ab, ST_TIMEOUT_FULL);
                 const uint8_t* st = wait_stage();
-                if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
-                if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, xs + c * KCHUNK, lane, acc1);
+                if (!touch_only) {
+                    if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
+                    if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, xs + c * KCHUNK, lane, acc1);
+                }
                 release_stage();
             }
             if (a0) {
@@ -1056,7 +1084,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         // (appended to the cache here), as fp32 in the spare region of xbuf.  The q/k/v words are
         // polled while the consumers are still in P1.
         const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
-        const unsigned hl_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
+        const unsigned hl_base = __ldcg(p.epoch_base);
         uint32_t lpar = 0;
         auto stage_q = [&](int l) {
             mbar_wait(smem_u32(sm.h_layer), lpar, ab, ST_TIMEOUT_GRID);
@@ -1277,6 +1305,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.ab = ab;
         co.warp = warp;
         co.lane = lane;
+        co.touch_only = p.touch_only != 0;
         unsigned epoch = 0;
         uint32_t xparity = 0, hparity = 0, mparity = 0, qparity = 0;
         const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
@@ -1285,11 +1314,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         const float* cosr = p.cos + pos_off;
         const float* sinr = p.sin + pos_off;
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
-        // epochs of this launch's flag-in-data handoffs: launch count * (layers + 2) + layer + 1; never 0
-        const unsigned ll_base = __ldcg(p.launch_count) * static_cast<unsigned>(p.n_layers + 2);
+        // epochs of this launch's flag-in-data handoffs: running base + layer + 1.  The base is a word the
+        // last CTA of every launch advances by (layers + 2), so epochs are unique and increasing over
+        // launches of any layer count that share the scratch; a zero-filled word never matches
+        const unsigned ll_base = __ldcg(p.epoch_base);
         bool need_barrier = false;  // a phase of this launch wrote data the next one reads
-        // epochs of this launch's exchanges: launch count * (layers + 2) + layer + 1; never 0
-        const unsigned tp_base = (p.tp_size > 1) ? __ldcg(p.tp_launch_count) * static_cast<unsigned>(p.n_layers + 2) : 0u;
+        // epochs of this launch's exchanges with the peers, same scheme on a word of their own (all ranks
+        // run the same launches, so their words agree)
+        const unsigned tp_base = (p.tp_size > 1) ? __ldcg(p.tp_epoch_base) : 0u;
 
         const __half* x_first = p.embed ? (p.embed + static_cast<size_t>(__ldcg(p.token_in)) * H) : p.x_in;
 
@@ -1688,17 +1720,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     // is a thread-to-thread exchange: store my partial row, tagged with this layer's
                     // epoch, into every peer's buffer (8-byte stores over NVLink), wait (bounded)
                     // for the N-1 counterparts' words to show the epoch, add the N partials in
-                    // rank order in fp32.  Buffers alternate with the layer's parity, so a slot is
+                    // rank order in fp32.  Slots alternate with the exchange's epoch parity -- consecutive
+                    // exchanges, also across launches and for any layer count, differ in it -- so a slot is
                     // rewritten only after its reader has sent its next word.
                     const TpLayout tl{H, p.tp_size};
                     const unsigned tp_epoch = tp_base + static_cast<unsigned>(l) + 1u;
-                    const int parity = l & 1;
+                    const int parity = static_cast<int>(tp_epoch & 1u);
                     if (me + tid * CS < nrows) {
                         const int row = g3a * GRAN + me + tid * CS;
                         const float mine = dsm::tree_sum<CS>(sm.recv, stride, tid);
                         for (int r = 0; r < p.tp_size; ++r)
                             if (r != p.tp_rank)
-                                st_ll(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(row) * 8,
+                                st_ll_sys(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(row) * 8,
                                       __float_as_uint(mine), tp_epoch);
                         // all counterparts' words in flight at once; re-read (bounded) until every epoch matches
                         const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(row) * 8;
@@ -1708,7 +1741,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 #pragma unroll
                             for (int r = 0; r < MAX_TP; ++r) {
                                 if (r < p.tp_size && r != p.tp_rank) {
-                                    w[r] = ld_ll(mybuf + tl.partial_off(parity, r));
+                                    w[r] = ld_ll_sys(mybuf + tl.partial_off(parity, r));
                                     ok = ok && (w[r].y == tp_epoch);
                                 }
                             }
@@ -1807,11 +1840,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     // pick the same winner (largest logit, lowest index on ties)
                     const TpLayout tl{H, p.tp_size};
                     const unsigned tp_epoch = tp_base + static_cast<unsigned>(p.n_layers) + 1u;
-                    const int parity = static_cast<int>((tp_base / static_cast<unsigned>(p.n_layers + 2)) & 1u);
+                    const int parity = static_cast<int>(__ldcg(p.tp_epoch_base + 1) & 1u);  // launches of this decoder so far
                     if (lane < p.tp_size && lane != p.tp_rank) {
                         unsigned char* dst = p.tp_peer[lane] + tl.pairs_off(parity, p.tp_rank);
-                        st_ll(dst, __float_as_uint(b), tp_epoch);
-                        st_ll(dst + 8, static_cast<unsigned>(bi), tp_epoch);
+                        st_ll_sys(dst, __float_as_uint(b), tp_epoch);
+                        st_ll_sys(dst + 8, static_cast<unsigned>(bi), tp_epoch);
                     }
                     float rb = -INFINITY;
                     int rbi = 0x7fffffff;
@@ -1820,8 +1853,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         rbi = bi;
                     } else if (lane < p.tp_size) {
                         const unsigned char* src = p.tp_peer[p.tp_rank] + tl.pairs_off(parity, lane);
-                        rb = __uint_as_float(wait_ll(src, tp_epoch, ab));
-                        rbi = static_cast<int>(wait_ll(src + 8, tp_epoch, ab));
+                        rb = __uint_as_float(wait_ll_sys(src, tp_epoch, ab));
+                        rbi = static_cast<int>(wait_ll_sys(src + 8, tp_epoch, ab));
                     }
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) {
@@ -1853,9 +1886,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     p.sync[0] = 0u;
                     p.sync[1] = 0u;
                     p.sync[3] = 0u;
-                    *p.launch_count = *p.launch_count + 1u;
+                    *p.epoch_base = *p.epoch_base + static_cast<unsigned>(p.n_layers) + 2u;
                     if (p.seq_inc) *p.seq_inc = seq + 1;
-                    if (p.tp_size > 1) *p.tp_launch_count = *p.tp_launch_count + 1u;
+                    if (p.tp_size > 1) {
+                        p.tp_epoch_base[0] = p.tp_epoch_base[0] + static_cast<unsigned>(p.n_layers) + 2u;
+                        p.tp_epoch_base[1] = p.tp_epoch_base[1] + 1u;
+                    }
                     __threadfence();
                 }
             }

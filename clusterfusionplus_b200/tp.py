@@ -186,12 +186,26 @@ class TPDecoder:
         else:
             self._enqueue()
 
+    def status(self) -> int:
+        """This decoder's device status word (0 = every launch so far ended normally; 7 = a peer never
+        answered within the kernel's bounded wait).  A blocking 4-byte read; not cleared."""
+        st = C.c_int(0)
+        check(lib.cf_decoder_status(self.handle, C.byref(st)))
+        return st.value
+
     def generate(self, first_token: int, seq_len: int, n_tokens: int) -> List[int]:
+        """Greedy rollout with one host read per token.  The status word is checked after every token:
+        a rank whose peer stopped answering would otherwise decode on with wrong tokens.  Callers that
+        drive step() themselves should poll status() the same way."""
         self.reset(seq_len, first_token)
         out = []
         for _ in range(n_tokens):
             self.step()
             out.append(int(self.token.item()))
+            code = self.status()
+            if code != 0:
+                raise RuntimeError(f"clusterfusion_b200: tensor-parallel decode stopped with device status {code} "
+                                   f"on rank {self.rank} after {len(out)} tokens (7 = a peer never answered)")
         return out
 
     def close(self) -> None:

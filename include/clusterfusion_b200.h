@@ -81,12 +81,18 @@ int cf_model_dims(int model, CfDims* out);
  * persistent grid, cluster size, TMA ring stages for `model`. */
 int cf_launch_info(int model, int* sm_count, int* grid, int* cluster, int* stages, int* smem_bytes);
 
-/* Reads the device status word of the current device (synchronises the device),
- * clears it and re-arms the barrier words if it was set.  *status = 0 when every
- * launch so far finished normally. */
+/* Reads the device status words of the current device -- the shared workspace of the layer
+ * calls, every decoder, and the static scratch of cf_pythia_decoder_layer_noalloc
+ * (synchronises the device) -- clears what was set and re-arms the barrier words.
+ * *status = 0 when every launch so far finished normally; otherwise the call returns
+ * CF_ERR_DEVICE and *status is 1-2 TMA ring, 3 grid barrier / flag wait, 4 cluster exchange,
+ * 5 bad seq_len, 6 drain, 7 tensor-parallel peer never answered. */
 int cf_get_status(int* status);
 
-/* Fused decoder layer, one token at batch 1.
+/* Fused decoder layer, one token at batch 1.  The first call with a given set of tensors
+ * builds and uploads their descriptor (tensor maps), so it allocates and cannot be recorded
+ * into a stream capture (CF_ERR_INVALID while capturing); later calls with the same tensors
+ * can.  The same holds for the split, attention_only, mlp_only and Llama entry points.
  * Replaces pythia_2b8_decoder_layer_sm120 / pythia_6b9_decoder_layer_sm120
  * (include/pybind.cpp:109-129,198-218; include/5090/pythia_6b9/pythia_kernel_dispatch.cu:4-236). */
 int cf_pythia_decoder_layer(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len, void* stream);
@@ -110,11 +116,14 @@ int cf_pythia_decoder_layer_split(int model, const CfLayerWeights* w, const CfLa
  *   Limits: the built-in models only (at most 32 heads, 4096 QKV columns, ffn 16384)
  *   on at most 160 CTAs; anything larger is rejected with CF_ERR_UNSUPPORTED.
  *   The first call on a device looks up the array's device address and the launch
- *   geometry; make that first call outside any stream capture.
+ *   geometry; make that first call outside any stream capture.  So must be every call
+ *   whose tensors differ from the previous call's: it uploads a new descriptor, which a
+ *   capture cannot record (such a call fails with CF_ERR_INVALID while capturing).
  *   All calls on a device share the one array and it keeps the previous call's
  *   contents (the words that must start at zero are cleared on `stream` each call):
  *   two calls whose kernels overlap on the GPU (different streams) race.
- *   Device-side status of these launches is not part of cf_get_status.
+ *   A device-side failure of these launches (a wait that ran out, a bad seq_len) is
+ *   kept in the array's status word until cf_get_status reports and clears it.
  * No counterpart in the reference (its dispatcher allocates five tensors per call:
  * include/5090/pythia_6b9/pythia_kernel_dispatch.cu:31-39). */
 int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const CfLayerIO* io, int64_t seq_len,
@@ -158,6 +167,22 @@ int cf_debug_run_phases(int model, const CfLayerWeights* w, const CfLayerIO* io,
  * elements; a launch that would not fit leaves it untouched.  NULL switches it
  * off.  No counterpart in the reference. */
 int cf_debug_set_trace(void* device_buffer, int64_t n_slots);
+
+/* Diagnostic: the streaming ceiling of the decode kernel's own machinery.  One launch of the
+ * persistent grid streams matrix [rows, cols] fp16 (rows a multiple of 8, cols a multiple of 256, at
+ * most 4096) through the same TMA ring, producer and row-GEMV consumers as the LM-head phase, with
+ * nothing to wait for but the data: rows are dotted with x [cols] and discarded (touch_only != 0:
+ * the consumers take and release each stage without the arithmetic).  rows * cols * 2 bytes over the
+ * launch time is the read bandwidth the kernel's structure can reach.  scratch_desc: 1 KB of device
+ * memory, 128-byte aligned, owned by the caller (the descriptor is uploaded there; the call
+ * synchronises `stream` once).  No counterpart in the reference. */
+int cf_debug_stream_rows(const void* matrix, int64_t rows, int64_t cols, const void* x, int touch_only,
+                         void* scratch_desc, void* stream);
+
+/* Diagnostic: device address and size of the static scratch of cf_pythia_decoder_layer_noalloc
+ * on the current device, and the byte offset of its status word (tests write a code there from
+ * the host to check that cf_get_status reports it).  Allocates nothing. */
+int cf_debug_noalloc_scratch(void** base, int64_t* bytes, int64_t* status_offset);
 
 /* Attention half: io->attn_output = dense(attention) + o_bias, io->mlp_intermediate =
  * gelu(up(post_ln(x))), io->k_new / io->v_new.  mlp_down_* of `w` may be NULL.
@@ -282,6 +307,11 @@ int cf_decoder_tail(int64_t handle, void* stream);
 /* After the caller gathered every shard's (max, idx): pick the winner into the
  * token word and advance seq_len. pairs_val/pairs_idx are device arrays of tp_size. */
 int cf_decoder_select_token(int64_t handle, const float* pairs_val, const int* pairs_idx, void* stream);
+/* The decoder's device status word (codes as in cf_get_status), read with a blocking 4-byte copy
+ * and not cleared.  A loop that already waits for every token (reads it on the host) can poll
+ * this cheaply to notice a tensor-parallel peer that stopped answering (7) instead of decoding on
+ * with wrong tokens. */
+int cf_decoder_status(int64_t handle, int* status);
 int cf_decoder_destroy(int64_t handle);
 
 /* -------------------------------------------------------------------------

@@ -145,3 +145,45 @@ def test_pythia_2b8_greedy_64_steps_identical(cuda_device):
     assert got == want, f"first mismatch at step {first_diff}; min top-2 gap of the oracle {min(gaps):.4g}, " \
                         f"gap at mismatch {gaps[first_diff]:.4g}"
     assert mx <= MAX_ABS and rl <= 5 * REL_L2, (mx, rl)
+
+
+def test_pythia_6b9_shapes_greedy_64_steps_identical(cuda_device):
+    """The configuration the headline number is timed on, as a parity case: Pythia-6.9B layer shapes
+    (hidden 4096, 32 heads x 128, ffn 16384, vocabulary 50432), 8 layers, every cache filled to 4096
+    rows of N(0, 1) fp16 history (33 attention chunks per head), whole-token launches replayed from a
+    CUDA graph: 64 greedy tokens identical to the fp32 oracle's on the same seeded tensors."""
+    import clusterfusion as cf
+    dev = cuda_device
+    shape = O.Shape("6b9-8l", 4096, 32, 128, 32, 16384, 50432, layers=8)
+    seed, ctx, steps = 2024, 4096, 64
+    layers = [O.make_layer_weights(shape, l, seed=seed, device=dev) for l in range(shape.layers)]
+    head = O.make_head_weights(shape, seed=seed, device=dev)
+    max_seq = ctx + steps + 2
+    om = O.OracleModel(shape, [{n: t.cpu() for n, t in w.items()} for w in layers],
+                       {n: t.cpu() for n, t in head.items()}, max_seq, round_io=False)
+    dec, ld, hd, caches = build_decoder(shape, layers, head, max_seq, dev, use_graph=True)
+    for l, (k, v) in enumerate(caches):
+        kk, vv = O.make_kv_cache(shape, ctx, max_seq, 900 + l, device=dev)
+        k.copy_(kk), v.copy_(vv)
+        om.load_cache(l, kk, vv, ctx)
+    om.seq_len = ctx
+    tok = otok = 4242
+    dec.reset(ctx, tok)
+    got, want, gaps = [], [], []
+    logits = None
+    for _ in range(steps):
+        dec.step()
+        got.append(int(dec.token.item()))
+        logits, _ = om.step(otok)
+        top2 = torch.topk(logits, 2).values
+        gaps.append((top2[0] - top2[1]).item())
+        otok = int(logits.argmax())
+        want.append(otok)
+    status = cf.device_status()
+    mx, rl = O.compare(dec.logits, logits)
+    dec.close()
+    first_diff = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), None)
+    assert status == 0
+    assert got == want, f"first mismatch at step {first_diff}; min top-2 gap of the oracle {min(gaps):.4g}, " \
+                        f"gap at mismatch {gaps[first_diff]:.4g}"
+    assert mx <= MAX_ABS and rl <= 5 * REL_L2, (mx, rl)

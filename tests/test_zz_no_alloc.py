@@ -76,6 +76,58 @@ def test_noalloc_matches_regular_entry_point_twice(cuda_device, model):
     assert cf.device_status() == 0
 
 
+def test_noalloc_device_status_is_reported(cuda_device):
+    """A device-side failure of a noalloc launch must reach the host.  The failure is made on the
+    host: a status code is copied into the static array's status word (what a kernel whose bounded
+    wait ran out would have left there); nothing on the GPU is made to wait or fault.  The next
+    noalloc call must not wipe it, cf_get_status must report it and clear it."""
+    import clusterfusionplus_b200 as cf
+    from clusterfusionplus_b200 import _lib
+    from clusterfusionplus_b200.decoder import _IntView
+    base, nbytes, off = C.c_void_p(), C.c_int64(0), C.c_int64(0)
+    _lib.check(_lib.lib.cf_debug_noalloc_scratch(C.byref(base), C.byref(nbytes), C.byref(off)))
+    assert base.value and 0 < off.value < nbytes.value
+    word = torch.as_tensor(_IntView(base.value + off.value, (1,)), device=cuda_device)
+    assert cf.device_status() == 0
+    word.fill_(3)                                   # "a flag wait ran out"
+    torch.cuda.synchronize()
+    s, w, x, k, v, cos, sin = make_case("2b8", 5, rows=7)
+    _call(_lib.lib.cf_pythia_decoder_layer_noalloc, cf.CF_PYTHIA_2B8, "noalloc", 5, x, w, k, v, cos, sin, s)
+    assert int(word.item()) == 3                    # the call left the earlier failure readable
+    with pytest.raises(RuntimeError, match="device status 3"):
+        cf.device_status()
+    assert int(word.item()) == 0 and cf.device_status() == 0
+
+
+def test_noalloc_new_tensors_refused_during_capture(cuda_device):
+    """A call whose tensors differ from the previous call's uploads a new descriptor from host memory;
+    recorded into a stream capture that copy would read a dead pointer at every replay, so the entry
+    point refuses it while the stream is capturing.  Nothing is launched or replayed here."""
+    import clusterfusionplus_b200 as cf
+    from clusterfusionplus_b200 import _lib
+    s, w, x, k, v, cos, sin = make_case("2b8", 5, rows=7, wseed=99)
+    _call(_lib.lib.cf_pythia_decoder_layer_noalloc, cf.CF_PYTHIA_2B8, "noalloc", 5, x, w, k, v, cos, sin, s)
+    k2, v2 = k.clone(), v.clone()                   # a tensor set the descriptor slot does not hold
+    out = torch.empty((1, s.hidden), dtype=torch.float16, device=x.device)
+    kn = torch.empty((1, s.heads, s.head_dim), dtype=torch.float16, device=x.device)
+    vn = torch.empty_like(kn)
+    ws, io = _structs(cf.CF_PYTHIA_2B8, s, w, x, k2, v2, cos, sin, out, kn, vn)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        g.capture_begin()
+        try:
+            rc = _lib.lib.cf_pythia_decoder_layer_noalloc(cf.CF_PYTHIA_2B8, C.byref(ws), C.byref(io), 5, side.cuda_stream)
+            msg = _lib.last_error()
+        finally:
+            g.capture_end()
+    assert rc != 0 and "capture" in msg, (rc, msg)
+    del g
+    torch.cuda.synchronize()
+    assert cf.device_status() == 0
+
+
 def test_noalloc_argument_errors(cuda_device):
     """Same argument checks as the regular entry point: no free cache row -> error, nothing launched."""
     import clusterfusionplus_b200 as cf
