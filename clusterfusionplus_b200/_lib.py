@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libclusterfusion_b200.so")
+# CLUSTERFUSION_B200_LIB names another build of the same library (A/B comparisons of kernel variants)
+LIB_PATH = os.environ.get("CLUSTERFUSION_B200_LIB") or os.path.join(_HERE, "lib", "libclusterfusion_b200.so")
 
 CF_PYTHIA_2B8 = 0
 CF_PYTHIA_6B9 = 1

@@ -313,14 +313,25 @@ int check_dims(const CfDims& d) {
 }
 
 // ring depth and activation buffer for one launch
-int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* nstage, int* xbuf_floats) {
+int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* nstage, int* xbuf_floats, int* aux_off) {
     const int KVW = d.heads * d.head_dim;
-    const int kc3 = ((p3_flags & F3_USE_O) ? ceil_div(KVW, KCHUNK) : 0) + ((p3_flags & F3_USE_DOWN) ? ceil_div(d.ffn, KCHUNK) : 0);
+    const int kco = (p3_flags & F3_USE_O) ? ceil_div(KVW, KCHUNK) : 0;
+    const int kc3 = kco + ((p3_flags & F3_USE_DOWN) ? ceil_div(d.ffn, KCHUNK) : 0);
     int xb = 2 * d.hidden;  // both LayerNorm outputs of a layer side by side
     if (ceil_div(kc3, cs) * KCHUNK > xb) xb = ceil_div(kc3, cs) * KCHUNK;
-    if (16 * d.head_dim + 32 > xb) xb = 16 * d.head_dim + 32;
-    // pre-staged queries of up to MAXL heads (q, new k, new v) behind the LayerNorm outputs
-    if (qpre_offset(d.hidden, d.head_dim) + MAXL * 3 * d.head_dim > xb) xb = qpre_offset(d.hidden, d.head_dim) + MAXL * 3 * d.head_dim;
+    // The auxiliary region (pre-staged queries + hand-over buffer of attention partials) must stay clear
+    // of the LayerNorm outputs and of the MLP chunks a CTA stages at the start of P3, which are the
+    // first (chunks it owns) - (attention chunks it owns) chunks of xbuf.
+    int nmid_max = 0;
+    for (int me = 0; me < cs; ++me) {
+        const int my3 = kc3 > me ? ceil_div(kc3 - me, cs) : 0, nattn = kco > me ? ceil_div(kco - me, cs) : 0;
+        if (my3 - nattn > nmid_max) nmid_max = my3 - nattn;
+    }
+    int aux = 2 * d.hidden;
+    if (nmid_max * KCHUNK > aux) aux = nmid_max * KCHUNK;
+    aux = (aux + 3) / 4 * 4;
+    if (aux + aux_floats(d.head_dim) > xb) xb = aux + aux_floats(d.head_dim);
+    *aux_off = aux;
     xb = (xb + 3) / 4 * 4;
     const long fixed = static_cast<long>(smem_bytes_for(0, xb));
     int ns = static_cast<int>((ds.smem_optin - fixed) / STAGE_BYTES);
@@ -378,7 +389,9 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         const int mode = env_int("CFB200_P1_MODE", -1);
         if (mode == 0 || mode == 2 || mode == 3 || (mode == 1 && ok)) p.p1_joint = mode;
     }
-    rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats);
+    rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats, &p.aux_off);
+    p.pf_stages = env_int("CFB200_LOOKAHEAD", 0);  // measured slower when issued at the end of P3 (experiments only)
+    if (p.pf_stages < 0) p.pf_stages = 0;
     if (rc != CF_OK) return rc;
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
     const void* fn = kernel_ptr(d.head_dim, c.cs);
@@ -732,8 +745,8 @@ int cf_launch_info(int model, int* sm_count, int* grid, int* cluster, int* stage
     if ((rc = get_device(&ds))) return rc;
     if ((rc = pick_cfg(*ds, d.head_dim))) return rc;
     const LaunchCfg& c = ds->cfg[d.head_dim == 128];
-    int ns = 0, xb = 0;
-    if ((rc = fit_smem(*ds, d, c.cs, F3_FULL, &ns, &xb))) return rc;
+    int ns = 0, xb = 0, aux = 0;
+    if ((rc = fit_smem(*ds, d, c.cs, F3_FULL, &ns, &xb, &aux))) return rc;
     if (sm_count) *sm_count = ds->sm_count;
     if (grid) *grid = c.grid;
     if (cluster) *cluster = c.cs;

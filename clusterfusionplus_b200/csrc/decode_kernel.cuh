@@ -57,6 +57,9 @@ constexpr int NTHREADS = NCTHR + 32 + NHTHR;  // consumers + producer warp + hel
 constexpr int KV_TILE = 128;                // cache rows per attention item (K tile and V tile are separate stages)
 constexpr int KV_RPH = KV_TILE / (2 * NCWARP);  // rows per half-warp per item
 constexpr int MAXL = 4;                     // attention partial slots per CTA
+constexpr int MAXHPC = 2;                   // heads one CTA's attention items can span (items per CTA <= chunks per head)
+constexpr int NFWARP = 2;                   // helper warps that finish attention partials (helper warps 1 .. NFWARP)
+constexpr int NFTHR = NFWARP * 32;
 constexpr int MAX_P3_ROWS = 128;            // output rows one cluster may own in P3
 constexpr int MAX_H = 4096;                 // LayerNorm register staging limit
 constexpr int WTS_SLOTS = 256;              // (attention chunk, head, partial) merge weights one CTA may need
@@ -118,6 +121,8 @@ struct Params {
     int p3_flags;
     int nstage;
     int xbuf_floats;
+    int aux_off;       // floats into xbuf: [MAXHPC][3][D] pre-staged q / new k / new v, then the partial hand-over buffer
+    int pf_stages;     // stages of the next phase the producer asks L2 to fetch ahead of the ring at a layer boundary
     // activations
     const __half* x_in;   // [H]; ignored when embed != nullptr
     const __half* embed;  // optional [V, H] table: x = embed[*token_in]
@@ -275,8 +280,6 @@ struct Smem {
     uint8_t* ring;
     float* xbuf;
     float* red;     // 64
-    float* q_s;     // 128: scaled, rotated query of the current head
-    float* kv_s;    // 256: new token's key (rotated) and value, fp16-rounded
     float* pm;      // WTS_SLOTS running maxima of the partials this CTA merges
     float* pl;      // WTS_SLOTS their denominators
     int* offs;      // WTS_SLOTS their offsets in the partial buffer (-1: none), fixed for a launch
@@ -290,12 +293,14 @@ struct Smem {
     uint64_t* mid_ready;   // helper thread -> consumers: every CTA is past P1, the MLP intermediate is complete
     uint64_t* h_layer;     // consumers -> helpers: a new layer has begun, xbuf's spare region is free
     uint64_t* q_ready;     // helpers -> consumers: this layer's rotated queries (and new k, v) are in xbuf
+    uint64_t* pf_ready;    // consumers -> helpers: a head's per-warp attention partials are in the hand-over buffer
+    uint64_t* pf_free;     // helpers -> consumers: the hand-over buffer has been read
     int* abort_flag;
 };
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 128 + 256 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 6) * 8 + 16;
+           (64 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 8) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -303,9 +308,7 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.ring = base;
     s.xbuf = reinterpret_cast<float*>(base + static_cast<size_t>(nstage) * STAGE_BYTES);
     s.red = s.xbuf + xbuf_floats;
-    s.q_s = s.red + 64;
-    s.kv_s = s.q_s + 128;
-    s.pm = s.kv_s + 256;
+    s.pm = s.red + 64;
     s.pl = s.pm + WTS_SLOTS;
     s.offs = reinterpret_cast<int*>(s.pl + WTS_SLOTS);
     s.part_s = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
@@ -318,13 +321,17 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.mid_ready = s.xbar + 3;
     s.h_layer = s.xbar + 4;
     s.q_ready = s.xbar + 5;
-    s.abort_flag = reinterpret_cast<int*>(s.xbar + 6);
+    s.pf_ready = s.xbar + 6;
+    s.pf_free = s.xbar + 7;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 8);
     return s;
 }
 
-// Where the helper warps leave the pre-staged queries in xbuf: behind both LayerNorm outputs
-// (live through P1) and behind P2's merge buffer; [MAXL][3][D] floats.
-__host__ __device__ __forceinline__ int qpre_offset(int H, int D) { return max(2 * H, 16 * D + 32); }
+// The auxiliary region of xbuf (Params::aux_off): the pre-staged queries [MAXHPC][3][D] that the helper
+// warps write while P1 still runs, then the hand-over buffer of attention partials (one slot per consumer
+// warp: D numerators, then NCWARP {max, denominator} pairs).  It lies behind both LayerNorm outputs (live
+// through P1) and behind the MLP chunks that P3 stages (written while a partial may still be in the buffer).
+__host__ __device__ __forceinline__ int aux_floats(int D) { return MAXHPC * 3 * D + NCWARP * D + 2 * NCWARP; }
 
 // ---------------------------------------------------------------- math helpers
 __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f)); }
@@ -717,27 +724,53 @@ struct Producer {
     uint64_t policy;
     AbortCtl ab;
     uint32_t issued;  // stages issued so far
+    // Look-ahead mode: a copy of the producer walks a phase's schedule without touching the ring and
+    // asks L2 to fetch the stages numbered [win_lo, win_hi) of that phase (the ring will take the
+    // first ones itself).  Used at a layer boundary, where every CTA spends microseconds in the
+    // epilogue, the hand-over of the hidden state and the LayerNorm while its ring is already full:
+    // DRAM would idle, and the next phase then starts with more than the ring's depth on chip.
+    bool ahead;
+    int sidx, win_lo, win_hi;
+    bool live;
 
+    __device__ __forceinline__ bool stop() const { return *ab.flag != 0 || (ahead && sidx >= win_hi); }
     __device__ __forceinline__ void acquire() {
+        if (ahead) {
+            live = sidx >= win_lo && sidx < win_hi;
+            ++sidx;
+            return;
+        }
         mbar_wait(empty_addr + cur.stage * 8, cur.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
+    }
+    __device__ __forceinline__ void expect(uint32_t bar, uint32_t bytes) {
+        if (!ahead) mbar_arrive_expect_tx(bar, bytes);
+    }
+    __device__ __forceinline__ void tile(uint32_t dst, const void* tm, int x, int y, uint32_t bar) {
+        if (!ahead) tma_load_2d(dst, tm, x, y, bar, policy);
+        else if (live) tma_prefetch_2d(tm, x, y);
+    }
+    __device__ __forceinline__ void stage_done() {
+        if (ahead) return;
+        cur.advance();
+        ++issued;
     }
     // n consecutive granules starting at granule g0, K offset kx, into consecutive slots at dst:
     // 64-row boxes, then 32-row boxes, then 8-row boxes
     __device__ __forceinline__ void issue_run(const WeightMaps* tm, int kx, int g0, int n, uint32_t dst, uint32_t bar) {
         int w = 0;
-        for (; w + 8 <= n; w += 8) tma_load_2d(dst + w * SLOT_BYTES, &tm->r64, kx, (g0 + w) * GRAN, bar, policy);
-        for (; w + 4 <= n; w += 4) tma_load_2d(dst + w * SLOT_BYTES, &tm->r32, kx, (g0 + w) * GRAN, bar, policy);
-        for (; w < n; ++w) tma_load_2d(dst + w * SLOT_BYTES, &tm->r8, kx, (g0 + w) * GRAN, bar, policy);
+        for (; w + 8 <= n; w += 8) tile(dst + w * SLOT_BYTES, &tm->r64, kx, (g0 + w) * GRAN, bar);
+        for (; w + 4 <= n; w += 4) tile(dst + w * SLOT_BYTES, &tm->r32, kx, (g0 + w) * GRAN, bar);
+        for (; w < n; ++w) tile(dst + w * SLOT_BYTES, &tm->r8, kx, (g0 + w) * GRAN, bar);
     }
     // one stage of `n` row granules (rows g0*8 ...) at K offset kx
     __device__ __forceinline__ void rows_stage(const WeightMaps* tm, int kx, int g0, int n) {
+        if (stop()) return;
         acquire();
         if (*ab.flag) return;
         const uint32_t bar = full_addr + cur.stage * 8;
-        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
+        expect(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
         issue_run(tm, kx, g0, n, ring_addr + cur.stage * STAGE_BYTES, bar);
-        cur.advance();
-        ++issued;
+        stage_done();
     }
     // all stages of a row-partitioned GEMV: granules [g0, g0+cnt) of `tm`, KC chunks each
     __device__ __forceinline__ void rows_phase(const WeightMaps* tm, int g0, int cnt, int KC) {
@@ -747,6 +780,7 @@ struct Producer {
         for (int r = 0; r < nr; ++r) {
             const int n = base + (r < extra ? 1 : 0);
             for (int c = 0; c < KC; ++c) rows_stage(tm, c * KCHUNK, g, n);
+            if (stop()) return;
             g += n;
         }
     }
@@ -762,15 +796,15 @@ struct Producer {
             const int n = base + (r < extra ? 1 : 0);
             const int nA = max(0, min(cntA - g, n));  // granules of this round that belong to A
             for (int c = 0; c < KC; ++c) {
+                if (stop()) return;
                 acquire();
                 if (*ab.flag) return;
                 const uint32_t bar = full_addr + cur.stage * 8;
-                mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
+                expect(bar, static_cast<uint32_t>(n) * SLOT_BYTES);
                 const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
                 if (nA > 0) issue_run(tmA, c * KCHUNK, gA0 + g, nA, dst, bar);
                 if (n > nA) issue_run(tmB, c * KCHUNK, gB0 + g + nA - cntA, n - nA, dst + nA * SLOT_BYTES, bar);
-                cur.advance();
-                ++issued;
+                stage_done();
             }
             g += n;
         }
@@ -925,6 +959,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         mbar_init(smem_u32(sm.mid_ready), 1);
         mbar_init(smem_u32(sm.h_layer), 1);
         mbar_init(smem_u32(sm.q_ready), NHWARP);
+        mbar_init(smem_u32(sm.pf_ready), NCWARP);
+        mbar_init(smem_u32(sm.pf_free), NFWARP);
         mbar_fence_init();
     }
     __syncthreads();
@@ -1010,6 +1046,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             pr.policy = l2_policy_evict_first();
             pr.ab = ab;
             pr.issued = 0;
+            pr.ahead = false;
+            pr.sidx = pr.win_lo = pr.win_hi = 0;
+            pr.live = false;
+            // stages [nstage, nstage + pf_stages) of layer l's P1 (or of the LM head) into L2
+            auto look_ahead = [&](int l) {
+                if (p.pf_stages <= 0) return;
+                Producer la = pr;
+                la.ahead = true;
+                la.sidx = 0;
+                la.win_lo = p.nstage;
+                la.win_hi = p.nstage + p.pf_stages;
+                if (l < p.n_layers) {
+                    if (p.phase_mask & PH_P1)
+                        la.rows_phase2(&p.layers[l].tm_qkv, qa, qb - qa, &p.layers[l].tm_up, ua, ub - ua, KC1);
+                } else if (p.phase_mask & PH_P4) {
+                    la.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
+                }
+            };
             for (int l = 0; l < p.n_layers; ++l) {
                 const LayerDesc* L = p.layers + l;
                 if (p.phase_mask & PH_P1) {
@@ -1036,6 +1090,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                     trace_mark(p, cta, l, TR_PROD_P3);
+                    // this layer's last tiles are on their way: the consumers now drain them, reduce, hand
+                    // the hidden state over and normalise -- time in which the ring is full and DRAM idle
+                    look_ahead(l + 1);
                 }
             }
             if (p.phase_mask & PH_P4) pr.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
@@ -1095,7 +1152,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const float* cosr = p.cos + pos_off;
             const float* sinr = p.sin + pos_off;
             const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
-            float* qpre = sm.xbuf + qpre_offset(H, D);
+            float* qpre = sm.xbuf + p.aux_off;
             const int h_first = t2a / nch, h_last = (t2b - 1) / nch;
             for (int h = h_first; h <= h_last; ++h) {
                 const bool has_last = (h + 1) * nch - 1 < t2b;
@@ -1180,10 +1237,75 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
             constexpr int ML_ITERS = (WTS_SLOTS + NHTHR - 1) / NHTHR;
             uint32_t gpar = 0;
+            unsigned nfin = 0;  // partials finished so far (all layers): phase of the hand-over barriers
+            // Helper warps 1..NFWARP finish this CTA's attention partials.  The consumers leave a head's
+            // per-warp running state (numerators, max, denominator) in the hand-over buffer and go on
+            // with the next head or with P3; here the NCWARP slots are combined in a fixed order, the
+            // token being decoded is folded in where this CTA streamed the head's last chunk (its
+            // rotated key and value are still in the pre-staged region), and the record is written and
+            // stamped for the CTAs that merge it.
+            auto finish_partials = [&](int l) {
+                const int ft = ht - 32;  // 0 .. NFTHR-1
+                const int h_first = t2a / nch, h_last = (t2b - 1) / nch;
+                const float* qpre = sm.xbuf + p.aux_off;
+                const float* hb = qpre + MAXHPC * 3 * D;   // [NCWARP][D]
+                const float* hml = hb + NCWARP * D;        // [NCWARP][2]
+                const unsigned pep = hl_base + static_cast<unsigned>(l) + 1u;
+                for (int h = h_first; h <= h_last; ++h) {
+                    const bool has_last = (h + 1) * nch - 1 < t2b;
+                    const float* hq = qpre + (h - h_first) * 3 * D;
+                    mbar_wait(smem_u32(sm.pf_ready), nfin & 1u, ab, ST_TIMEOUT_GRID);
+                    float s_new = -INFINITY;
+                    if (has_last) {
+                        // score of the new token: q (already scaled) . k_new, summed in a fixed order
+                        float part = 0.f;
+                        for (int d = ft; d < D; d += NFTHR) part = fmaf(hq[d], hq[D + d], part);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                        if (lane == 0) sm.red[40 + (ft >> 5)] = part;
+                        fin_sync();
+                        s_new = 0.f;
+#pragma unroll
+                        for (int i = 0; i < NFWARP; ++i) s_new += sm.red[40 + i];
+                    }
+                    float M = s_new;
+#pragma unroll
+                    for (int i = 0; i < NCWARP; ++i) M = fmaxf(M, hml[i * 2]);
+                    float wgt[NCWARP], lsum = 0.f;
+#pragma unroll
+                    for (int i = 0; i < NCWARP; ++i) {
+                        const float mi = hml[i * 2];
+                        wgt[i] = (mi > -INFINITY) ? exp2f(mi - M) : 0.f;
+                        lsum = fmaf(hml[i * 2 + 1], wgt[i], lsum);
+                    }
+                    const float wn = has_last ? exp2f(s_new - M) : 0.f;
+                    lsum += wn;
+                    float* dst = p.attn_part + (static_cast<size_t>(cta) * MAXL + (h - h_first)) * PREC;
+                    for (int d = ft; d < D; d += NFTHR) {
+                        float a = 0.f;
+#pragma unroll
+                        for (int i = 0; i < NCWARP; ++i) a = fmaf(hb[i * D + d], wgt[i], a);
+                        if (has_last) a = fmaf(wn, hq[2 * D + d], a);
+                        dst[d] = a;
+                    }
+                    if (ft == 0) {
+                        dst[D] = M;
+                        dst[D + 1] = lsum;
+                    }
+                    fin_sync();  // record written, hand-over buffer read by everybody
+                    if (ft == 0) publish_record(dst + D + 2, pep);
+                    if (lane == 0) mbar_arrive(smem_u32(sm.pf_free));
+                    ++nfin;
+                }
+            };
             for (int l = 0; l < p.n_layers; ++l) {
                 if (do_q) stage_q(l);
+                if (do_q && ht >= 32 && ht < 32 + NFTHR) finish_partials(l);
                 if (p.phase_mask & PH_P3) watch_mid(l);
-                if (!do_merge) continue;
+                if (!do_merge) {
+                    if (do_q) helper_sync(NHTHR);  // the pre-staged region is rewritten only after its last reader
+                    continue;
+                }
                 // the consumers have left P2 of this layer: xbuf's attention chunks are free
                 mbar_wait(smem_u32(sm.h_go), gpar, ab, ST_TIMEOUT_GRID);
                 gpar ^= 1u;
@@ -1308,6 +1430,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.touch_only = p.touch_only != 0;
         unsigned epoch = 0;
         uint32_t xparity = 0, hparity = 0, mparity = 0, qparity = 0;
+        unsigned nflush = 0;  // attention partials handed to the helper warps so far (all layers)
         const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
         const int pos_off = p.rope_stride * seq;
@@ -1450,61 +1573,60 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 // cached rows: items [t2a, t2b), head-major
                 const int hw = lane >> 4, l16 = lane & 15;
                 const bool dim_ok = l16 * 8 < D;
-                float* mbuf = sm.xbuf;                 // [16][D]
-                float* mlbuf = sm.xbuf + 16 * D;       // [16][2]
+                float* hbuf = sm.xbuf + p.aux_off + MAXHPC * 3 * D;  // hand-over buffer: [NCWARP][D]
+                float* hml = hbuf + NCWARP * D;                      // [NCWARP][2]
                 int cur_h = -1;
                 float qreg[8], acc[8], m_run = -INFINITY, l_run = 0.f;
-                const int h_first = (t2b > t2a) ? t2a / nch : 0;
-                const float* qpre = sm.xbuf + qpre_offset(H, D);
+                const float* qpre = sm.xbuf + p.aux_off;
                 const float* hq = qpre;
                 if (do_q) {
                     mbar_wait(smem_u32(sm.q_ready), qparity, ab, ST_TIMEOUT_GRID);
                     qparity ^= 1u;
                 }
 
-                auto flush = [&](int h) {
-                    const int slot = warp * 2 + hw;
-                    if (dim_ok) {
+                // A head is finished (or this CTA's items end): the two half-warps of a warp join their
+                // running states in registers, the warp leaves one slot in the hand-over buffer and
+                // signals the helper warps, which combine the slots, fold in the new token, write and
+                // stamp the record.  The consumers do not wait for that; only the next use of the
+                // buffer waits (bounded) until the helpers have read the previous one.
+                auto flush = [&]() {
+                    const float mo = __shfl_xor_sync(0xffffffffu, m_run, 16);
+                    const float lo = __shfl_xor_sync(0xffffffffu, l_run, 16);
+                    const float M = fmaxf(m_run, mo);
+                    const float ws = (m_run > -INFINITY) ? exp2f(m_run - M) : 0.f;
+                    const float wo = (mo > -INFINITY) ? exp2f(mo - M) : 0.f;
+                    float a2[8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) mbuf[slot * D + l16 * 8 + k] = acc[k];
+                    for (int k = 0; k < 8; ++k) {
+                        const float ao = __shfl_xor_sync(0xffffffffu, acc[k], 16);
+                        // the same expression on both half-warps: lower half first
+                        a2[k] = (hw == 0) ? fmaf(acc[k], ws, ao * wo) : fmaf(ao, wo, acc[k] * ws);
                     }
-                    if (l16 == 0) {
-                        mlbuf[slot * 2] = m_run;
-                        mlbuf[slot * 2 + 1] = l_run;
-                    }
-                    consumer_sync(NCTHR);
-                    float* dst = p.attn_part + (static_cast<size_t>(cta) * MAXL + (h - h_first)) * PREC;
-                    if (tid < D) {
-                        float M = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) M = fmaxf(M, mlbuf[i * 2]);
-                        float a = 0.f, lsum = 0.f;
-                        if (M > -INFINITY) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const float w = exp2f(mlbuf[i * 2] - M);
-                                a = fmaf(mbuf[i * D + tid], w, a);
-                                lsum = fmaf(mlbuf[i * 2 + 1], w, lsum);
-                            }
+                    const float l2 = (hw == 0) ? fmaf(l_run, ws, lo * wo) : fmaf(lo, wo, l_run * ws);
+                    if (nflush > 0) mbar_wait(smem_u32(sm.pf_free), (nflush - 1u) & 1u, ab, ST_TIMEOUT_GRID);
+                    if (hw == 0) {
+                        if (dim_ok) {
+                            *reinterpret_cast<float4*>(hbuf + warp * D + l16 * 8) = make_float4(a2[0], a2[1], a2[2], a2[3]);
+                            *reinterpret_cast<float4*>(hbuf + warp * D + l16 * 8 + 4) = make_float4(a2[4], a2[5], a2[6], a2[7]);
                         }
-                        dst[tid] = a;
-                        if (tid == 0) {
-                            dst[D] = M;
-                            dst[D + 1] = lsum;
+                        if (l16 == 0) {
+                            hml[warp * 2] = M;
+                            hml[warp * 2 + 1] = l2;
                         }
                     }
-                    consumer_sync(NCTHR);
-                    if (tid == 0) publish_record(dst + D + 2, pep);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(sm.pf_ready));
+                    ++nflush;
                 };
 
                 for (int t = t2a; t < t2b; ++t) {
                     const int h = t / nch, ch = t - h * nch;
                     if (h != cur_h) {
-                        if (cur_h >= 0) flush(cur_h);
+                        if (cur_h >= 0) flush();
                         cur_h = h;
                         // the helper warps staged q (and the new k, v where this CTA streams the
                         // head's last chunk) while P1 was still running
-                        hq = qpre + (h - h_first) * 3 * D;
+                        hq = qpre + (h - t2a / nch) * 3 * D;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
                             qreg[k] = dim_ok ? hq[l16 * 8 + k] : 0.f;
@@ -1575,26 +1697,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                     co.release_stage();
-                    // the token being decoded: one extra row after the head's last chunk
-                    if (ch == nch - 1 && warp == 0 && hw == 0) {
-                        float sn = 0.f;
-                        if (dim_ok) {
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) sn = fmaf(qreg[k], hq[D + l16 * 8 + k], sn);
-                        }
-#pragma unroll
-                        for (int o = 8; o > 0; o >>= 1) sn += __shfl_xor_sync(0x0000ffffu, sn, o);
-                        const float mx = fmaxf(m_run, sn);
-                        const float sc = exp2f(m_run - mx), pn = exp2f(sn - mx);
-                        l_run = fmaf(l_run, sc, pn);
-                        if (dim_ok) {
-#pragma unroll
-                            for (int k = 0; k < 8; ++k) acc[k] = fmaf(acc[k], sc, pn * hq[2 * D + l16 * 8 + k]);
-                        }
-                        m_run = mx;
-                    }
+                    // (the token being decoded is folded in by the helper warps when they finish the partial)
                 }
-                if (cur_h >= 0) flush(cur_h);
+                if (cur_h >= 0) flush();
                 if (tid == 0) trace_mark(p, cta, l, TR_P2_DONE);
                 need_barrier = true;
             }

@@ -135,6 +135,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
         : "memory");
 }
 
+// The same tile brought into L2 only: no shared-memory destination, no completion signal.
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -158,6 +164,11 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 // named barrier over the helper warps only
 __device__ __forceinline__ void helper_sync(int nthreads) {
     asm volatile("bar.sync 2, %0;" ::"r"(nthreads) : "memory");
+}
+
+// named barrier over the helper warps that finish attention partials
+__device__ __forceinline__ void fin_sync() {
+    asm volatile("bar.sync 3, 64;" ::: "memory");
 }
 
 // named barrier over the consumer warps only (the producer warp never joins)
