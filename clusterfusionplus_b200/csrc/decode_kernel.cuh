@@ -283,16 +283,15 @@ struct Smem {
     float* pm;      // WTS_SLOTS running maxima of the partials this CTA merges
     float* pl;      // WTS_SLOTS their denominators
     int* offs;      // WTS_SLOTS their offsets in the partial buffer (-1: none), fixed for a launch
-    float* part_s;  // MAX_P3_ROWS
     float* recv;    // MAX_P3_ROWS
     uint64_t* full;
     uint64_t* empty;
     uint64_t* xbar;
     uint64_t* h_go;        // consumers -> helpers: this CTA has entered P3, xbuf's attention chunks are free
     uint64_t* attn_ready;  // helpers -> consumers: merged attention chunks are in xbuf
-    uint64_t* mid_ready;   // helper thread -> consumers: every CTA is past P1, the MLP intermediate is complete
+    uint64_t* mid_ready;   // helper warp 0 -> consumers: every CTA is past P1 and this CTA's MLP chunks are staged in xbuf
     uint64_t* h_layer;     // consumers -> helpers: a new layer has begun, xbuf's spare region is free
-    uint64_t* q_ready;     // helpers -> consumers: this layer's rotated queries (and new k, v) are in xbuf
+    uint64_t* q_ready;     // [MAXHPC] helpers -> consumers: the rotated query of the i-th head this CTA streams is in xbuf
     uint64_t* pf_ready;    // consumers -> helpers: a head's per-warp attention partials are in the hand-over buffer
     uint64_t* pf_free;     // helpers -> consumers: the hand-over buffer has been read
     int* abort_flag;
@@ -300,7 +299,7 @@ struct Smem {
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 3 * WTS_SLOTS + MAX_P3_ROWS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 8) * 8 + 16;
+           (64 + 3 * WTS_SLOTS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 9) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -311,8 +310,7 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.pm = s.red + 64;
     s.pl = s.pm + WTS_SLOTS;
     s.offs = reinterpret_cast<int*>(s.pl + WTS_SLOTS);
-    s.part_s = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
-    s.recv = s.part_s + MAX_P3_ROWS;
+    s.recv = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
     s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
     s.empty = s.full + MAX_STAGES;
     s.xbar = s.empty + MAX_STAGES;
@@ -320,10 +318,10 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.attn_ready = s.xbar + 2;
     s.mid_ready = s.xbar + 3;
     s.h_layer = s.xbar + 4;
-    s.q_ready = s.xbar + 5;
-    s.pf_ready = s.xbar + 6;
-    s.pf_free = s.xbar + 7;
-    s.abort_flag = reinterpret_cast<int*>(s.xbar + 8);
+    s.q_ready = s.xbar + 5;  // and + 6
+    s.pf_ready = s.xbar + 7;
+    s.pf_free = s.xbar + 8;
+    s.abort_flag = reinterpret_cast<int*>(s.xbar + 9);
     return s;
 }
 
@@ -953,12 +951,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             mbar_init(smem_u32(sm.full + s), 1);
             mbar_init(smem_u32(sm.empty + s), NCWARP);
         }
-        mbar_init(smem_u32(sm.xbar), CS > 1 ? CS - 1 : 1);
+        mbar_init(smem_u32(sm.xbar), NCWARP * CS);
         mbar_init(smem_u32(sm.h_go), 1);
         mbar_init(smem_u32(sm.attn_ready), NHWARP);
         mbar_init(smem_u32(sm.mid_ready), 1);
         mbar_init(smem_u32(sm.h_layer), 1);
-        mbar_init(smem_u32(sm.q_ready), NHWARP);
+        for (int i = 0; i < MAXHPC; ++i) mbar_init(smem_u32(sm.q_ready + i), NHWARP);
         mbar_init(smem_u32(sm.pf_ready), NCWARP);
         mbar_init(smem_u32(sm.pf_free), NFWARP);
         mbar_fence_init();
@@ -1034,6 +1032,61 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         g4a = part_begin(cta, NG4, G);
         g4b = part_begin(cta + 1, NG4, G);
     }
+
+    // This CTA's MLP chunks of P3's activation vector, fp32 in xbuf, chunk-major from offset 0: copied
+    // (or, for SwiGLU, formed as silu(gate) * up) from the fp32 intermediate that P1 left in global
+    // memory.  Called by `nthr` threads with t = 0 .. nthr-1; copies are asynchronous (the caller
+    // waits with cp.async.wait_all).
+    auto stage_mid = [&](int t, int nthr) {
+        const int nmid_ = my3 - nattn;
+        const int nvec = nmid_ * (KCHUNK / 4);
+        if (p.arch_flags & AF_SWIGLU) {
+            // mid[e] = silu(gate[e]) * up[e], gate rows at [0, F), up rows at [F, 2F) of the scratch
+            for (int v0 = t; v0 < nvec; v0 += nthr * 4) {
+                float4 gv[4], uv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * nthr;
+                    gv[u] = uv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (v < nvec) {
+                        const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                        const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;  // F is a multiple of 8
+                        if (e < F) {
+                            gv[u] = ld_cg_f32x4(p.mid_f32 + e);
+                            uv[u] = ld_cg_f32x4(p.mid_f32 + F + e);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * nthr;
+                    if (v < nvec) {
+                        const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                        float4 o;
+                        o.x = gv[u].x / (1.f + __expf(-gv[u].x)) * uv[u].x;
+                        o.y = gv[u].y / (1.f + __expf(-gv[u].y)) * uv[u].y;
+                        o.z = gv[u].z / (1.f + __expf(-gv[u].z)) * uv[u].z;
+                        o.w = gv[u].w / (1.f + __expf(-gv[u].w)) * uv[u].w;
+                        *reinterpret_cast<float4*>(sm.xbuf + i * KCHUNK + k4 * 4) = o;
+                    }
+                }
+            }
+        } else {
+            // asynchronous 16-byte copies of the fp32 intermediate straight into xbuf
+            for (int v = t; v < nvec; v += nthr) {
+                const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
+                const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;
+                float* dst = sm.xbuf + i * KCHUNK + k4 * 4;
+                if (e + 3 < F) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
+                                 "l"(p.mid_f32 + e) : "memory");
+                } else {
+                    for (int k = 0; k < 4; ++k) dst[k] = (e + k < F) ? ld_cg_f32(p.mid_f32 + e + k) : 0.f;
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+    };
 
     // =========================================================== producer warp
     if (warp == NCWARP) {
@@ -1127,12 +1180,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         // every CTA past P1 <=> the MLP intermediate is complete: one helper thread watches the
         // count and tells the consumers through shared memory, so that they never poll global memory
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
+        // Helper warp 0: one thread watches the count, then the warp copies this CTA's MLP chunks into
+        // xbuf -- the consumers are in P2 meanwhile (xbuf's chunk area is free once every CTA, this one
+        // included, is past P1) and find their P3 operands in place when they arrive.
         auto watch_mid = [&](int l) {
-            if (mid_wait && ht == 0) {
-                const unsigned target = static_cast<unsigned>(l + 1) * static_cast<unsigned>(G);
-                wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(p.sync + 3) >= target; }, ab, ST_TIMEOUT_GRID);
-                __threadfence();
-                mbar_arrive(smem_u32(sm.mid_ready));
+            if (mid_wait && ht < 32) {
+                if (ht == 0) {
+                    const unsigned target = static_cast<unsigned>(l + 1) * static_cast<unsigned>(G);
+                    wait_bounded<POLL_BACKOFF_NS>([&] { return ld_acquire_u32(p.sync + 3) >= target; }, ab, ST_TIMEOUT_GRID);
+                    __threadfence();
+                }
+                __syncwarp();
+                stage_mid(ht, 32);
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                __syncwarp();
+                if (ht == 0) mbar_arrive(smem_u32(sm.mid_ready));
             }
         };
         const bool do_merge = (p.phase_mask & PH_P3) && nattn > 0;
@@ -1154,22 +1216,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
             float* qpre = sm.xbuf + p.aux_off;
             const int h_first = t2a / nch, h_last = (t2b - 1) / nch;
-            for (int h = h_first; h <= h_last; ++h) {
-                const bool has_last = (h + 1) * nch - 1 < t2b;
+            const int half_r = R >> 1;
+            // elements [e_lo, e_hi) of head h's [q; k; v] vector: rotate, scale / round, leave in xbuf
+            // (and, for k and v, in the cache row and the k_new / v_new outputs)
+            auto stage_range = [&](int h, int e_lo, int e_hi) {
                 const int qi = h * 3 * D;
                 float* dst = qpre + (h - h_first) * 3 * D;
                 // all of this thread's words (and their rotation partners) in flight at once; the
                 // epochs are checked together and the batch is re-read (bounded) until all match
-                const int ne = has_last ? 3 * D : D;
-                const int half_r = R >> 1;
-                constexpr int KQ = (3 * D + NHTHR - 1) / NHTHR;
+                constexpr int KQ = (2 * D + NHTHR - 1) / NHTHR;
                 uint2 w[KQ], wp[KQ];
                 auto fetch = [&]() {
                     bool ok = true;
 #pragma unroll
                     for (int k = 0; k < KQ; ++k) {
-                        const int e = ht + k * NHTHR;
-                        if (e < ne) {
+                        const int e = e_lo + ht + k * NHTHR;
+                        if (e < e_hi) {
                             const int part = e / D, d = e - part * D;
                             w[k] = ld_ll(qkv.base + qi + e);
                             ok = ok && (qkv.any || w[k].y == qkv.epoch);
@@ -1184,8 +1246,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (!fetch()) wait_bounded<POLL_BACKOFF_NS>(fetch, ab, ST_TIMEOUT_PEER);
 #pragma unroll
                 for (int k = 0; k < KQ; ++k) {
-                    const int e = ht + k * NHTHR;
-                    if (e >= ne) continue;
+                    const int e = e_lo + ht + k * NHTHR;
+                    if (e >= e_hi) continue;
                     const int part = e / D, d = e - part * D;
                     float val = __uint_as_float(w[k].x);
                     if (part < 2 && d < R) {
@@ -1207,9 +1269,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                 }
+            };
+            // the queries first, head by head, each released to the consumers as soon as it is there ...
+            for (int h = h_first; h <= h_last; ++h) {
+                stage_range(h, 0, D);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(sm.q_ready + (h - h_first)));
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(sm.q_ready));
+            // ... then the new token's key and value where this CTA streams the head's last chunk: only the
+            // helper warps that finish the partials need them
+            for (int h = h_first; h <= h_last; ++h)
+                if ((h + 1) * nch - 1 < t2b) stage_range(h, D, 3 * D);
+            helper_sync(NHTHR);
         };
         {
             // Which partial feeds which of my chunks depends only on (grid, seq): tabulate once.
@@ -1429,7 +1500,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.lane = lane;
         co.touch_only = p.touch_only != 0;
         unsigned epoch = 0;
-        uint32_t xparity = 0, hparity = 0, mparity = 0, qparity = 0;
+        uint32_t xparity = 0, hparity = 0, mparity = 0, qpar0 = 0, qpar1 = 0;
         unsigned nflush = 0;  // attention partials handed to the helper warps so far (all layers)
         const bool do_q = (p.phase_mask & PH_P2) && nch > 0 && t2b > t2a;
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
@@ -1579,10 +1650,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 float qreg[8], acc[8], m_run = -INFINITY, l_run = 0.f;
                 const float* qpre = sm.xbuf + p.aux_off;
                 const float* hq = qpre;
-                if (do_q) {
-                    mbar_wait(smem_u32(sm.q_ready), qparity, ab, ST_TIMEOUT_GRID);
-                    qparity ^= 1u;
-                }
 
                 // A head is finished (or this CTA's items end): the two half-warps of a warp join their
                 // running states in registers, the warp leaves one slot in the hand-over buffer and
@@ -1626,7 +1693,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         cur_h = h;
                         // the helper warps staged q (and the new k, v where this CTA streams the
                         // head's last chunk) while P1 was still running
-                        hq = qpre + (h - t2a / nch) * 3 * D;
+                        const int hi = h - t2a / nch;  // 0 or 1
+                        hq = qpre + hi * 3 * D;
+                        mbar_wait(smem_u32(sm.q_ready + hi), hi ? qpar1 : qpar0, ab, ST_TIMEOUT_GRID);
+                        if (hi) qpar1 ^= 1u;
+                        else qpar0 ^= 1u;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
                             qreg[k] = dim_ok ? hq[l16 * 8 + k] : 0.f;
@@ -1718,53 +1789,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 // them while the GEMV already runs over the MLP chunks.
                 const int nmid = my3 - nattn;
                 if (tid == 0) mbar_arrive(smem_u32(sm.h_go));
-                if (p.arch_flags & AF_SWIGLU) {
-                    // mid[e] = silu(gate[e]) * up[e], gate rows at [0, F), up rows at [F, 2F) of the scratch
-                    const int nvec = nmid * (KCHUNK / 4);
-                    for (int v0 = tid; v0 < nvec; v0 += NCTHR * 4) {
-                        float4 gv[4], uv[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int v = v0 + u * NCTHR;
-                            gv[u] = uv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (v < nvec) {
-                                const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
-                                const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;  // F is a multiple of 8
-                                if (e < F) {
-                                    gv[u] = ld_cg_f32x4(p.mid_f32 + e);
-                                    uv[u] = ld_cg_f32x4(p.mid_f32 + F + e);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int v = v0 + u * NCTHR;
-                            if (v < nvec) {
-                                const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
-                                float4 o;
-                                o.x = gv[u].x / (1.f + __expf(-gv[u].x)) * uv[u].x;
-                                o.y = gv[u].y / (1.f + __expf(-gv[u].y)) * uv[u].y;
-                                o.z = gv[u].z / (1.f + __expf(-gv[u].z)) * uv[u].z;
-                                o.w = gv[u].w / (1.f + __expf(-gv[u].w)) * uv[u].w;
-                                *reinterpret_cast<float4*>(sm.xbuf + i * KCHUNK + k4 * 4) = o;
-                            }
-                        }
-                    }
+                if (mid_wait) {
+                    // staged by helper warp 0 while this CTA was still in P2
                 } else if (!(p.p3_flags & F3_MID_F16)) {
-                    // asynchronous 16-byte copies of the fp32 intermediate straight into xbuf
-                    const int nvec = nmid * (KCHUNK / 4);
-                    for (int v = tid; v < nvec; v += NCTHR) {
-                        const int i = v / (KCHUNK / 4), k4 = v % (KCHUNK / 4);
-                        const int e = (me + (nattn + i) * CS - KCo) * KCHUNK + k4 * 4;
-                        float* dst = sm.xbuf + i * KCHUNK + k4 * 4;
-                        if (e + 3 < F) {
-                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)),
-                                         "l"(p.mid_f32 + e) : "memory");
-                        } else {
-                            for (int k = 0; k < 4; ++k) dst[k] = (e + k < F) ? ld_cg_f32(p.mid_f32 + e + k) : 0.f;
-                        }
-                    }
-                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    stage_mid(tid, NCTHR);
                 } else {
                     for (int i0 = 0; i0 < nmid; i0 += 8) {
                         float v[8];
@@ -1798,20 +1826,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
 
                 const int cnt = g3b - g3a;
                 const int nrows = cnt * GRAN;
+                const int stride = MAX_P3_ROWS / CS;
+                // every finished partial row goes straight from the lane that holds it to the CTA of the
+                // cluster that owns the row (dsm.cuh); no CTA-wide barrier on the way
                 if (cnt > 0) {
                     if (my3 > 0) {
-                        float* ps = sm.part_s;
-                        co.rows_phase(cnt, my3, sm.xbuf, [&](int g, int r, float v) { ps[g * GRAN + r] = v; },
+                        float* rv = sm.recv;
+                        co.rows_phase(cnt, my3, sm.xbuf,
+                                      [&](int g, int r, float v) { dsm::scatter_row<CS>(rv, stride, me, g * GRAN + r, v); },
                                       nattn > 0 ? nmid : -1, smem_u32(sm.attn_ready), hparity);
                     } else {
-                        for (int t = tid; t < nrows; t += NCTHR) sm.part_s[t] = 0.f;
+                        for (int t = tid; t < nrows; t += NCTHR) dsm::scatter_row<CS>(sm.recv, stride, me, t, 0.f);
                     }
                 }
                 else if (nattn > 0) mbar_wait(smem_u32(sm.attn_ready), hparity, ab, ST_TIMEOUT_FULL);  // keep phases paired
                 hparity ^= 1u;
+                dsm::exchange_arrive<CS>(sm.xbar, me, lane);
                 if (tid == 0) trace_mark(p, cta, l, TR_P3_GEMV);
-                const int stride = MAX_P3_ROWS / CS;
-                dsm::reduce_scatter_push<CS>(sm.part_s, sm.recv, stride, nrows, sm.xbar, xparity, tid, NCTHR, ab);
+                dsm::exchange_wait(sm.xbar, xparity, ab);
                 xparity ^= 1u;
                 // one output row per thread at most (MAX_P3_ROWS / CS <= consumer threads)
                 if (p.tp_size <= 1) {

@@ -5,10 +5,11 @@
 // redesigned:
 //   * fp32 end to end (the reference adds fp16 pairs with __hadd2),
 //   * a push reduce-scatter instead of a recursive-doubling all-reduce: each
-//     CTA stores the slice another CTA owns straight into that CTA's receive
-//     buffer (st.shared::cluster), signals it with one release-arrive on an
-//     mbarrier in the owner's shared memory, and the owner adds the CS slices
-//     in a fixed pairwise tree, so the result does not depend on arrival order,
+//     CTA stores the rows another CTA owns straight into that CTA's receive
+//     buffer (st.shared::cluster) from the thread that finished the row, every
+//     warp signals with one release-arrive per CTA on an mbarrier in the owner's
+//     shared memory, and the owner adds the CS slices in a fixed pairwise tree,
+//     so the result does not depend on arrival order,
 //   * no hardware cluster barrier on the data path: the only waits are bounded
 //     mbarrier waits, so the producer warp that streams weights is never held.
 //
@@ -65,49 +66,46 @@ __device__ __forceinline__ float tree_sum(const float* recv, int stride, int idx
     }
 }
 
-// Reduce-scatter of `nrows` fp32 partials across the CS CTAs of the cluster.
+// Reduce-scatter of fp32 partial rows across the CS CTAs of the cluster, without a CTA-wide barrier.
 //
-//   partial   : this CTA's partial sums, nrows floats, shared memory
 //   recv      : this CTA's receive buffer, CS slices of `stride` floats each
-//   xbar      : this CTA's exchange mbarrier (initialised with count CS - 1)
-//   parity    : phase parity of this use of xbar (caller toggles it per use)
-//   tid/nthr  : index of the calling thread among the `nthr` consumer threads
+//   xbar      : this CTA's exchange mbarrier, initialised with count NWARP * CS: every warp of every
+//               CTA of the cluster (this one included) arrives once per exchange
 //
-// On return recv[c * stride + i] holds CTA c's partial for the row this CTA owns
-// at slice index i; the caller sums them with tree_sum<CS>().  All `nthr`
-// consumer threads must call it.  Returns false if the wait was abandoned.
+// The thread that holds the finished partial of row t calls scatter_row(): it stores the value into
+// slot [me][t / CS] of the receive buffer of the CTA that owns the row (t % CS) -- its own shared memory
+// or, through distributed shared memory, a peer's.  When a warp has scattered all its rows it calls
+// exchange_arrive(): one lane release-arrives on every CTA's exchange barrier, which (through the warp
+// barrier before it) publishes the warp's stores.  exchange_wait() then returns once all NWARP * CS
+// arrivals of this exchange are in: recv[c * stride + i] holds CTA c's partial of the row this CTA owns
+// at slice index i, and the caller sums them with tree_sum<CS>().
 template <int CS>
-__device__ __forceinline__ bool reduce_scatter_push(const float* partial, float* recv, int stride, int nrows,
-                                                    uint64_t* xbar, uint32_t parity, int tid, int nthr,
-                                                    const AbortCtl& ab) {
-    const uint32_t me = (CS > 1) ? cta_rank() : 0u;
-    consumer_sync(nthr);  // partial[] complete
-    for (int t = tid; t < nrows; t += nthr) {
-        const uint32_t owner = static_cast<uint32_t>(t) % CS;
-        float* slot = recv + me * stride + t / CS;
-        if (owner == me) {
-            *slot = partial[t];
-        } else {
-            st_remote_f32(map_to_rank(smem_u32(slot), owner), partial[t]);
-        }
-    }
-    if constexpr (CS > 1) {
-        consumer_sync(nthr);  // all remote stores of this CTA issued
-        if (tid == 0) {
-            fence_acq_rel_cluster();
-            const uint32_t bar = smem_u32(xbar);
-#pragma unroll
-            for (uint32_t c = 0; c < CS; ++c)
-                if (c != me) arrive_remote_release(map_to_rank(bar, c));
-        }
-        const uint32_t bar = smem_u32(xbar);
-        bool ok = wait_bounded([&] { return mbar_try_wait_cluster(bar, parity); }, ab, ST_TIMEOUT_CLUSTER);
-        consumer_sync(nthr);
-        return ok;
+__device__ __forceinline__ void scatter_row(float* recv, int stride, uint32_t me, int t, float v) {
+    const uint32_t owner = static_cast<uint32_t>(t) % CS;
+    float* slot = recv + me * stride + t / CS;
+    if (owner == me) {
+        *slot = v;
     } else {
-        consumer_sync(nthr);
-        return true;
+        st_remote_f32(map_to_rank(smem_u32(slot), owner), v);
     }
+}
+
+template <int CS>
+__device__ __forceinline__ void exchange_arrive(uint64_t* xbar, uint32_t me, int lane) {
+    __syncwarp();
+    if (lane == 0) {
+        const uint32_t bar = smem_u32(xbar);
+#pragma unroll
+        for (uint32_t c = 0; c < CS; ++c) {
+            if (c == me) asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+            else arrive_remote_release(map_to_rank(bar, c));
+        }
+    }
+}
+
+__device__ __forceinline__ bool exchange_wait(uint64_t* xbar, uint32_t parity, const AbortCtl& ab) {
+    const uint32_t bar = smem_u32(xbar);
+    return wait_bounded([&] { return mbar_try_wait_cluster(bar, parity); }, ab, ST_TIMEOUT_CLUSTER);
 }
 
 }  // namespace dsm
