@@ -390,8 +390,6 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         if (mode == 0 || mode == 2 || mode == 3 || (mode == 1 && ok)) p.p1_joint = mode;
     }
     rc = fit_smem(ds, d, c.cs, p.p3_flags, &p.nstage, &p.xbuf_floats, &p.aux_off);
-    p.pf_stages = env_int("CFB200_LOOKAHEAD", 0);  // measured slower when issued at the end of P3 (experiments only)
-    if (p.pf_stages < 0) p.pf_stages = 0;
     if (rc != CF_OK) return rc;
     const size_t smem = smem_bytes_for(p.nstage, p.xbuf_floats);
     const void* fn = kernel_ptr(d.head_dim, c.cs);

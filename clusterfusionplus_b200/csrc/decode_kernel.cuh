@@ -122,7 +122,6 @@ struct Params {
     int nstage;
     int xbuf_floats;
     int aux_off;       // floats into xbuf: [MAXHPC][3][D] pre-staged q / new k / new v, then the partial hand-over buffer
-    int pf_stages;     // stages of the next phase the producer asks L2 to fetch ahead of the ring at a layer boundary
     // activations
     const __half* x_in;   // [H]; ignored when embed != nullptr
     const __half* embed;  // optional [V, H] table: x = embed[*token_in]
@@ -722,33 +721,15 @@ struct Producer {
     uint64_t policy;
     AbortCtl ab;
     uint32_t issued;  // stages issued so far
-    // Look-ahead mode: a copy of the producer walks a phase's schedule without touching the ring and
-    // asks L2 to fetch the stages numbered [win_lo, win_hi) of that phase (the ring will take the
-    // first ones itself).  Used at a layer boundary, where every CTA spends microseconds in the
-    // epilogue, the hand-over of the hidden state and the LayerNorm while its ring is already full:
-    // DRAM would idle, and the next phase then starts with more than the ring's depth on chip.
-    bool ahead;
-    int sidx, win_lo, win_hi;
-    bool live;
-
-    __device__ __forceinline__ bool stop() const { return *ab.flag != 0 || (ahead && sidx >= win_hi); }
+    __device__ __forceinline__ bool stop() const { return *ab.flag != 0; }
     __device__ __forceinline__ void acquire() {
-        if (ahead) {
-            live = sidx >= win_lo && sidx < win_hi;
-            ++sidx;
-            return;
-        }
         mbar_wait(empty_addr + cur.stage * 8, cur.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
     }
-    __device__ __forceinline__ void expect(uint32_t bar, uint32_t bytes) {
-        if (!ahead) mbar_arrive_expect_tx(bar, bytes);
-    }
+    __device__ __forceinline__ void expect(uint32_t bar, uint32_t bytes) { mbar_arrive_expect_tx(bar, bytes); }
     __device__ __forceinline__ void tile(uint32_t dst, const void* tm, int x, int y, uint32_t bar) {
-        if (!ahead) tma_load_2d(dst, tm, x, y, bar, policy);
-        else if (live) tma_prefetch_2d(tm, x, y);
+        tma_load_2d(dst, tm, x, y, bar, policy);
     }
     __device__ __forceinline__ void stage_done() {
-        if (ahead) return;
         cur.advance();
         ++issued;
     }
@@ -778,7 +759,6 @@ struct Producer {
         for (int r = 0; r < nr; ++r) {
             const int n = base + (r < extra ? 1 : 0);
             for (int c = 0; c < KC; ++c) rows_stage(tm, c * KCHUNK, g, n);
-            if (stop()) return;
             g += n;
         }
     }
@@ -1099,24 +1079,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             pr.policy = l2_policy_evict_first();
             pr.ab = ab;
             pr.issued = 0;
-            pr.ahead = false;
-            pr.sidx = pr.win_lo = pr.win_hi = 0;
-            pr.live = false;
-            // stages [nstage, nstage + pf_stages) of layer l's P1 (or of the LM head) into L2
-            auto look_ahead = [&](int l) {
-                if (p.pf_stages <= 0) return;
-                Producer la = pr;
-                la.ahead = true;
-                la.sidx = 0;
-                la.win_lo = p.nstage;
-                la.win_hi = p.nstage + p.pf_stages;
-                if (l < p.n_layers) {
-                    if (p.phase_mask & PH_P1)
-                        la.rows_phase2(&p.layers[l].tm_qkv, qa, qb - qa, &p.layers[l].tm_up, ua, ub - ua, KC1);
-                } else if (p.phase_mask & PH_P4) {
-                    la.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
-                }
-            };
+
             for (int l = 0; l < p.n_layers; ++l) {
                 const LayerDesc* L = p.layers + l;
                 if (p.phase_mask & PH_P1) {
@@ -1143,9 +1106,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                         }
                     }
                     trace_mark(p, cta, l, TR_PROD_P3);
-                    // this layer's last tiles are on their way: the consumers now drain them, reduce, hand
-                    // the hidden state over and normalise -- time in which the ring is full and DRAM idle
-                    look_ahead(l + 1);
                 }
             }
             if (p.phase_mask & PH_P4) pr.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);

@@ -135,12 +135,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
         : "memory");
 }
 
-// The same tile brought into L2 only: no shared-memory destination, no completion signal.
-__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y)
-                 : "memory");
-}
-
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
