@@ -240,7 +240,10 @@ def tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp
     ranks must agree on them; rank 0 then decodes the same steps on ONE GPU over the unsharded
     tensors and compares tokens (a mismatch at a step whose top-2 logit gap is below NEAR_TIE_GAP
     is reported as a near tie: the two decoders add the partial sums in different orders) and the
-    first step's hidden state (max-abs 2e-2, relative L2 1e-3)."""
+    first step's final hidden state.  The path's tolerance (max-abs 2e-2, relative L2 1e-3) is stated
+    for ONE layer against the fp32 oracle; here two fp16 pipelines are compared after `layers` layers,
+    each of which rounds the hidden state to fp16, so both bounds are scaled by sqrt(layers)."""
+    scale = max(1.0, float(args.layers)) ** 0.5
     dec.reset(args.ctx, 17)
     toks, hid0 = [], None
     for i in range(PARITY_STEPS):
@@ -273,7 +276,8 @@ def tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp
         out.update({"equals_single_gpu": first is None or near_tie, "first_mismatch": first,
                     "mismatch_is_near_tie": near_tie if first is not None else None,
                     "min_top2_gap": min(gaps), "hidden_max_abs": herr[0], "hidden_rel_l2": herr[1],
-                    "hidden_within_tolerance": herr[0] <= 2e-2 and herr[1] <= 1e-3})
+                    "hidden_tolerance": {"max_abs": 2e-2 * scale, "rel_l2": 1e-3 * scale},
+                    "hidden_within_tolerance": herr[0] <= 2e-2 * scale and herr[1] <= 1e-3 * scale})
     dist.barrier()
     return out
 
@@ -559,6 +563,85 @@ def run_llama_stack(args):
     }))
 
 
+def run_llama_batch(args):
+    """Secondary line (BASELINE config 5 at batch 4 / 16): one decode step of --batch sequences through a
+    Llama-2-7B-shaped stack of --layers layers -- the batched, paged attention block (reference entry point
+    llama_decoder_layer_batch_decode_sglang) followed by the batched SwiGLU MLP block -- 2 launches per
+    layer replayed as one CUDA graph.  Every sequence has --llama-ctx cached rows per layer, scattered over
+    a shuffled token pool."""
+    import clusterfusionplus_b200 as cf
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    H, NH, D, F, S, L, B = 4096, 32, 128, 11008, args.llama_ctx, args.layers, args.batch
+    g = torch.Generator(device=dev)
+    g.manual_seed(4321)
+    layers, pools = [], []
+    n_rows = B * (S + 1)
+    for _ in range(L):
+        layers.append(dict(wqkv=rand_half((3 * H, H), g, dev), wo=rand_half((H, H), g, dev), g1=rand_half((H,), g, dev, 1.0),
+                           wgu=rand_half((2 * F, H), g, dev), wd=rand_half((H, F), g, dev), g2=rand_half((H,), g, dev, 1.0)))
+        pools.append((rand_half((n_rows, H), g, dev, std=1.0), rand_half((n_rows, H), g, dev, std=1.0)))
+    perm = torch.randperm(n_rows, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    indptr = torch.arange(0, B + 1, dtype=torch.int32) * (S + 1)
+    indptr, indices = indptr.to(dev), perm.to(dev)
+    kptrs = torch.tensor([p[0].data_ptr() for p in pools], dtype=torch.int64, device=dev)
+    vptrs = torch.tensor([p[1].data_ptr() for p in pools], dtype=torch.int64, device=dev)
+    positions = torch.full((B,), S, dtype=torch.int64, device=dev)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.outer(torch.arange(S + 1, dtype=torch.float32), inv)
+    cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous().to(dev)
+    x0, r0 = rand_half((B, H), g, dev, std=1.0), rand_half((B, H), g, dev, std=1.0)
+    bufs = [torch.empty(B, H, dtype=torch.float16, device=dev) for _ in range(4)]
+
+    def step():
+        x, r = x0, r0
+        for l, w in enumerate(layers):
+            cf.llama_decoder_layer_batch_decode_sglang(bufs[0], bufs[1], x, r, w["wqkv"], w["wo"], indptr, indices, kptrs, vptrs, l,
+                                                       w["g1"], 1e-5, positions, cos_sin)
+            x, r = cf.llama_mlp_batch_sglang(bufs[0], bufs[1], w["wgu"], w["wd"], w["g2"], 1e-5)
+        return x
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()  # scratch allocation and tensor maps outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    sampler = ClockSampler(0)
+    for _ in range(args.warmup):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.summary(t0, time.perf_counter())
+    us = e0.elapsed_time(e1) / args.steps * 1e3
+    per_layer = 2 * (3 * H * H + H * H + 3 * H * F) + B * 2 * 2 * S * H + 2 * (2 * H) + B * 2 * H * 8  # weights, KV, norms, activations
+    peak, src = hbm_peak()
+    gbs = per_layer * L / (us * 1e-6) / 1e9
+    print(json.dumps({
+        "metric": "Llama-2-7B-shaped layer stack, batched decode step (us)", "value": us, "unit": "us/step", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
+        "dtype": "fp16 weights/KV/activations, fp32 accumulate (tcgen05)", "data": "synthetic",
+        "config": {"workload": f"{L} layers x (paged attention block + SwiGLU MLP 4096-11008-4096), batch {B}, {S} cached rows "
+                               f"per sequence and layer in a shuffled token pool", "batch": B,
+                   "l2": "per-step working set far larger than L2"},
+        "tokens_per_s": B / (us * 1e-6),
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": src,
+                     "algorithmic_bytes_per_step": per_layer * L, "traffic": None,
+                     "kernel": "llama_batch_kernel (tcgen05 skinny GEMMs + paged attention), 2 launches per layer"},
+        "gpu_launches": 2 * L * args.steps, "clocks": clocks, "device_status": cf.device_status(),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -579,6 +662,9 @@ def main():
     ap.add_argument("--llama-ctx", type=int, default=0,
                     help="instead of Pythia decode: one step through a Llama-2-7B-shaped layer stack with this many "
                          "cached rows per layer (1 GPU, batch 1; a secondary line)")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="with --llama-ctx: decode sequences per step; > 1 (or --llama-batched) uses the batched, paged blocks")
+    ap.add_argument("--llama-batched", action="store_true", help="with --llama-ctx: the batched, paged blocks even at batch 1")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="instead of decode: time prompt ingestion of this many tokens (1 GPU; a secondary line)")
     args = ap.parse_args()
@@ -587,7 +673,10 @@ def main():
         run_prefill(args)
         return
     if args.llama_ctx > 0:
-        run_llama_stack(args)
+        if args.batch > 1 or args.llama_batched:
+            run_llama_batch(args)
+        else:
+            run_llama_stack(args)
         return
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

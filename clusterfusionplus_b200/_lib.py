@@ -66,6 +66,9 @@ SIGNATURES = {
     "cf_pythia_decoder_layer_noalloc": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
     "cf_llama_decoder_layer_sglang": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]
                                       + [C.c_void_p] * 5),
+    "cf_llama_decoder_layer_batch_sglang": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p,
+                                                       C.c_int64, C.c_void_p]),
+    "cf_llama_mlp_batch_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_llama_mlp_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_debug_run_phases": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_int, C.c_void_p]),
     "cf_debug_set_trace": (C.c_int, [C.c_void_p, C.c_int64]),

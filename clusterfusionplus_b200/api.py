@@ -209,6 +209,59 @@ def llama_mlp_sglang(input, residual, gate_up_weight, down_weight, rms_weight, e
     return out, residual
 
 
+def llama_decoder_layer_batch_decode_sglang(output, residual_output, input, residual, weight_qkv, weight_o,
+                                            paged_kv_indptr, paged_kv_indices, k_cache_ptrs, v_cache_ptrs, layer_id,
+                                            rms_input_weight, eps, positions, cos_sin):
+    """The Llama-2-7B attention block for a batch of decode sequences over a paged KV pool; writes into
+    `output` and `residual_output` ([batch, 4096] fp16 each) and returns None, like the reference.
+    input / residual [batch, 4096] fp16; paged_kv_indptr [batch + 1] and paged_kv_indices int32 (one pool row per
+    token; a sequence's last entry is the slot the new key / value go to); k_cache_ptrs / v_cache_ptrs: int64 /
+    uint64 device tensors with one pool pointer per layer ([pool_rows, 4096] fp16 pools); positions [batch] int64;
+    cos_sin [max_position, 128] fp32 (64 cosines, 64 sines per row).
+    Reference: llama_decoder_layer_batch_sglang_sm120, include/pybind.cpp:90-106,282."""
+    H = 4096
+    if input.dim() != 2 or input.shape[1] != H:
+        raise RuntimeError(f"input: expected [batch, {H}], got {tuple(input.shape)}")
+    B = int(input.shape[0])
+
+    def ptrs(t, name):
+        if t.dtype not in (torch.int64, torch.uint64):
+            raise RuntimeError(f"{name}: expected an int64 / uint64 tensor of device pointers, got {t.dtype}")
+        if int(layer_id) < 0 or int(layer_id) >= t.numel():
+            raise RuntimeError(f"layer_id {layer_id} outside {name} ({t.numel()} entries)")
+        return _req(t, name, t.numel(), t.dtype)
+
+    if paged_kv_indptr.numel() != B + 1:
+        raise RuntimeError(f"paged_kv_indptr: expected {B + 1} entries, got {paged_kv_indptr.numel()}")
+    if cos_sin.dim() != 2 or cos_sin.shape[1] != 128:
+        raise RuntimeError(f"cos_sin: expected [positions, 128] fp32, got {tuple(cos_sin.shape)}")
+    check(lib.cf_llama_decoder_layer_batch_sglang(
+        _req(output, "output", B * H), _req(residual_output, "residual_output", B * H), _req(input, "input", B * H),
+        _req(residual, "residual", B * H), _req(weight_qkv, "weight_qkv", 3 * H * H), _req(weight_o, "weight_o", H * H),
+        _req(paged_kv_indptr, "paged_kv_indptr", B + 1, torch.int32),
+        _req(paged_kv_indices, "paged_kv_indices", paged_kv_indices.numel(), torch.int32),
+        ptrs(k_cache_ptrs, "k_cache_ptrs"), ptrs(v_cache_ptrs, "v_cache_ptrs"), int(layer_id),
+        _req(rms_input_weight, "rms_input_weight", H), float(eps), _req(positions, "positions", B, torch.int64),
+        _req(cos_sin, "cos_sin", cos_sin.numel(), torch.float32), B, _stream()))
+    return None
+
+
+def llama_mlp_batch_sglang(input, residual, gate_up_weight, down_weight, rms_weight, eps):
+    """(output [batch, 4096], residual_out [batch, 4096]) of the SwiGLU MLP block for a batch of rows, weights streamed
+    once for all rows (see llama_mlp_sglang for the arithmetic).  `residual` is not modified."""
+    H = 4096
+    B = int(input.shape[0])
+    ffn = int(down_weight.shape[-1])
+    opts = dict(dtype=torch.float16, device=input.device)
+    out = torch.empty((B, H), **opts)
+    res_out = torch.empty((B, H), **opts)
+    check(lib.cf_llama_mlp_batch_sglang(
+        _req(input, "input", B * H), _req(residual, "residual", B * H), _req(gate_up_weight, "gate_up_weight", 2 * ffn * H),
+        _req(down_weight, "down_weight", H * ffn), _req(rms_weight, "rms_weight", H), float(eps), ffn, B,
+        out.data_ptr(), res_out.data_ptr(), _stream()))
+    return out, res_out
+
+
 # ---------------------------------------------------------------------------- contexts
 class _DeviceView:
     """Zero-copy torch view of a buffer the C library owns."""

@@ -23,6 +23,7 @@
 
 #include "../../include/clusterfusion_b200.h"
 #include "decode_kernel.cuh"
+#include "host_common.h"
 #include "prefill_gemm.h"
 
 using namespace cfb;
@@ -285,6 +286,10 @@ int get_device(DeviceState** out) {
     if (prop.major != 10)
         return fail(CF_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major,
                     prop.minor);
+    {
+        const int ns = env_int("CFB200_POLL_BACKOFF_NS", -1);
+        if (ns >= 0) CF_CUDA(cudaMemcpyToSymbol(c_poll_backoff_ns, &ns, sizeof(int)));
+    }
     DeviceState* ds = new DeviceState();
     ds->dev = dev;
     ds->sm_count = prop.multiProcessorCount;
@@ -725,6 +730,19 @@ int noalloc_setup(NoAllocDevice** out) {
 
 }  // namespace
 
+// ---- helpers shared with the other translation units (host_common.h)
+CfEncodeTiledFn cf_host_encode_fn() { return get_encode(); }
+int cf_host_fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+int cf_host_refuse_in_capture(cudaStream_t st, const char* what) { return refuse_upload_in_capture(st, what); }
+
 // =============================================================================
 extern "C" {
 
@@ -782,6 +800,11 @@ int cf_get_status(int* status) {
         if (ds->dev >= 0 && ds->dev < NOALLOC_MAX_DEVICES && g_noalloc[ds->dev].ready &&
             (rc = probe(g_noalloc[ds->dev].ds.ws)))
             return rc;
+    }
+    {
+        int s = 0;
+        if ((rc = cf_host_lb_probe_status(ds->dev, &s))) return rc;
+        if (s != 0) worst = s;
     }
     *status = worst;
     if (worst != 0)

@@ -88,6 +88,10 @@ __device__ __forceinline__ void raise_abort(const AbortCtl& a, int code) {
     atomicCAS(a.status, 0, code);
 }
 
+// Pause between two probes of a word in global memory that has not arrived yet, in nanoseconds
+// (CFB200_POLL_BACKOFF_NS overrides it when the library first touches a device).
+__constant__ int c_poll_backoff_ns = 96;
+
 // Spin on `probe()` until it returns true, the CTA has aborted, or the time
 // limit passes.  Returns false when the wait was abandoned.
 // BACKOFF_NS > 0 sleeps between probes: for polls of global memory, where many waiting threads
@@ -100,7 +104,7 @@ __device__ __forceinline__ bool wait_bounded(Probe probe, const AbortCtl& a, int
     uint32_t it = 0;
     constexpr uint32_t CHECK_MASK = BACKOFF_NS > 0 ? 0xfu : 0xffu;
     while (!probe()) {
-        if constexpr (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
+        if constexpr (BACKOFF_NS > 0) __nanosleep(c_poll_backoff_ns);
         if ((++it & CHECK_MASK) == 0) {
             if (*a.flag) return false;
             if (globaltimer_ns() - t0 > wait_limit_ns(code)) {

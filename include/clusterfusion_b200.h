@@ -138,8 +138,10 @@ int cf_pythia_decoder_layer_noalloc(int model, const CfLayerWeights* w, const Cf
  * post-RoPE, [32,128].  residual_out must not alias residual.
  * Replaces llama_decoder_layer_sglang_sm120 (include/pybind.cpp:75-86;
  * include/5090/llama/llama_kernel_sglang_dispatch.cu:4-151; kernel_sglang.cuh:20-634).
- * The reference's other Llama entry points (transposed-weight llama_decoder_layer, paged
- * batch llama_decoder_layer_batch_decode_sglang) are not provided. */
+ * The paged batch entry point is cf_llama_decoder_layer_batch_sglang below; the reference's
+ * transposed-weight llama_decoder_layer (include/pybind.cpp:66-74) is not provided: it computes the same
+ * block from weights stored [in, out], a layout none of the reference's tests or benchmarks exercise; a
+ * caller that holds such weights transposes them once when loading. */
 int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const void* weight_qkv,
                                   const void* weight_o, const void* k_cache, const void* v_cache, int64_t seq_len,
                                   const void* rms_input_weight, float eps, const float* cos, const float* sin,
@@ -153,6 +155,35 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
  * caller (tests/test_llama.py:108-110 has it commented out); a full Llama layer needs it. */
 int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
                         const void* rms_weight, float eps, int64_t ffn, void* output, void* residual_out, void* stream);
+
+/* Llama-2-7B attention block for a BATCH of 1..16 decode sequences over a paged KV pool, one launch.
+ * Per sequence b: residual_output[b] = input[b] + residual[b] (fp16; residual may be NULL);
+ * h = RMSNorm(residual_output[b], rms_input_weight, eps); q,k,v = weight_qkv h (rows [Q of all heads;
+ * K of all heads; V of all heads]); rotate-half RoPE with the angles of row positions[b] of cos_sin
+ * ([positions, 128] fp32: 64 cosines, then 64 sines).  Sequence b owns the pool rows
+ * paged_kv_indices[paged_kv_indptr[b] .. paged_kv_indptr[b+1]) -- one row = one token, [4096] fp16 --
+ * of the pools k_cache_ptrs[layer_id] / v_cache_ptrs[layer_id] (device arrays of device pointers): the LAST
+ * entry is the slot the new key / value are written to, the entries before it are the history that is
+ * attended to (plus the new token); every sequence needs at least that one entry.
+ * output[b] = weight_o attention(b).  All tensors [batch, 4096] fp16 unless said otherwise; indptr /
+ * indices int32, positions int64.  The weights are streamed once for the whole batch: the projections run
+ * as skinny GEMMs on the tensor cores (tcgen05), the rest as in the batch-1 block.  The first call on a
+ * device allocates 2.3 MB of scratch (not capturable); calls on one device share it and must not overlap.
+ * Replaces llama_decoder_layer_batch_sglang_sm120 (include/pybind.cpp:90-106,282;
+ * include/5090/llama/llama_kernel_batch_sglang_dispatch.cu:6-111; kernel_batch_sglang.cuh:43-664). */
+int cf_llama_decoder_layer_batch_sglang(void* output, void* residual_output, const void* input, const void* residual,
+                                        const void* weight_qkv, const void* weight_o, const int* paged_kv_indptr,
+                                        const int* paged_kv_indices, const uint64_t* k_cache_ptrs,
+                                        const uint64_t* v_cache_ptrs, int layer_id, const void* rms_input_weight, float eps,
+                                        const int64_t* positions, const float* cos_sin, int64_t batch, void* stream);
+
+/* The SwiGLU MLP block (see cf_llama_mlp_sglang) for a batch of 1..16 rows, weights streamed once:
+ * residual_out[b] = input[b] + residual[b]; output[b] = (silu(y Wg^T) * (y Wu^T)) Wd^T with
+ * y = RMSNorm(residual_out[b]) * rms_weight.  ffn must be a multiple of 64.  No counterpart in the
+ * reference, which leaves the MLP to its caller (tests/test_llama.py:108-110). */
+int cf_llama_mlp_batch_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
+                              const void* rms_weight, float eps, int64_t ffn, int64_t batch, void* output,
+                              void* residual_out, void* stream);
 
 /* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
  * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one

@@ -45,6 +45,38 @@ def llama_attn_block_fp32(x, residual, weight_qkv, weight_o, k_cache, v_cache, r
     return attn @ f(weight_o).t(), s, k_new[None].clone(), v_new[None].clone()
 
 
+def llama_attn_block_batch_fp32(x, residual, weight_qkv, weight_o, k_pool, v_pool, indptr, indices, positions, cos_sin,
+                                rms_weight, eps, heads: int = 32, head_dim: int = 128):
+    """The batched, paged form of the block (llama_decoder_layer_batch_decode_sglang, include/pybind.cpp:90-106;
+    page-table semantics of include/5090/llama/kernel_batch_sglang.cuh:118-123, 322-323, 343-371): sequence b owns the
+    pool rows indices[indptr[b] : indptr[b+1]] (one row = one token of all heads); the LAST of them is the slot the
+    new token's key / value are written to, the ones before it are its history.  cos_sin [positions, head_dim] holds
+    the cos of the head_dim/2 rotation angles of a position, then their sin; positions[b] selects the row.
+    Every sequence goes through llama_attn_block_fp32 (pinned against transformers) on its gathered history.
+    Returns (output [B,H], residual_out [B,H], k_new [B,NH,D], v_new [B,NH,D], slots [B]) in fp32 / int64."""
+    f = lambda t: t.detach().to("cpu", torch.float32)
+    ip = indptr.detach().cpu().long().tolist()
+    ix = indices.detach().cpu().long()
+    pos = positions.detach().cpu().long().tolist()
+    cs = f(cos_sin)
+    half = head_dim // 2
+    outs, ress, kns, vns, slots = [], [], [], [], []
+    for b in range(len(ip) - 1):
+        rows = ix[ip[b]:ip[b + 1] - 1]
+        c, sn = cs[pos[b], :half], cs[pos[b], half:head_dim]
+        o, s, kn, vn = llama_attn_block_fp32(x[b:b + 1], residual[b:b + 1], weight_qkv, weight_o, f(k_pool)[rows], f(v_pool)[rows],
+                                             rms_weight, eps, torch.cat([c, c]), torch.cat([sn, sn]), heads, head_dim)
+        outs.append(o), ress.append(s), kns.append(kn), vns.append(vn), slots.append(int(ix[ip[b + 1] - 1]))
+    return torch.cat(outs), torch.cat(ress), torch.cat(kns), torch.cat(vns), torch.tensor(slots)
+
+
+def llama_mlp_block_batch_fp32(x, residual, gate_up_weight, down_weight, rms_weight, eps):
+    """llama_mlp_block_fp32 row by row: (out [B,H], residual_out [B,H])."""
+    outs, ress = zip(*[llama_mlp_block_fp32(x[b:b + 1], residual[b:b + 1], gate_up_weight, down_weight, rms_weight, eps)
+                       for b in range(x.shape[0])])
+    return torch.cat(outs), torch.cat(ress)
+
+
 def hf_llama_attn_block(x, residual, weight_qkv, weight_o, k_cache, v_cache, rms_weight, eps, cos, sin,
                         heads: int = 32, head_dim: int = 128):
     """The same block through transformers' LlamaRMSNorm + LlamaAttention (eager, fp32)."""

@@ -142,3 +142,35 @@ def test_llama_oracle_reproduces_golden(case):
         out, res = L.llama_mlp_block_fp32(t["x"], t["res"], t["wgu"], t["wd"], t["g"], G.LLAMA_EPS)
     np.testing.assert_array_equal(res.numpy(), gold["residual"])
     np.testing.assert_allclose(out.numpy(), gold["out"], atol=1e-5, rtol=1e-5)
+
+
+def test_llama_batch_oracle_gathers_through_the_page_table():
+    """The batched oracle is the pinned single-sequence oracle applied to every sequence's gathered history: a
+    shuffled page table must give the same result as contiguous caches, and the slot is the sequence's last entry."""
+    from oracle import llama_oracle as LO
+    torch.manual_seed(0)
+    heads, hd = 4, 128
+    Hs = heads * hd
+    lengths = [5, 0, 9]
+    wqkv, wo = torch.randn(3 * Hs, Hs) * 0.05, torch.randn(Hs, Hs) * 0.05
+    g1 = 1 + 0.02 * torch.randn(Hs)
+    n_rows = sum(lengths) + len(lengths) + 3
+    kpool, vpool = torch.randn(n_rows, Hs).half(), torch.randn(n_rows, Hs).half()
+    perm = torch.randperm(n_rows)
+    indptr, idx, at = [0], [], 0
+    for s_ in lengths:
+        idx.append(perm[at:at + s_ + 1]); at += s_ + 1; indptr.append(indptr[-1] + s_ + 1)
+    indices = torch.cat(idx)
+    x, res = torch.randn(3, Hs).half(), torch.randn(3, Hs).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    ang = torch.outer(torch.arange(16).float(), inv)
+    cs = torch.cat([ang.cos(), ang.sin()], dim=1)
+    pos = torch.tensor(lengths)
+    o, s, kn, vn, slots = LO.llama_attn_block_batch_fp32(x, res, wqkv, wo, kpool, vpool, torch.tensor(indptr), indices, pos, cs,
+                                                         g1, 1e-5, heads, hd)
+    assert slots.tolist() == [int(indices[indptr[b + 1] - 1]) for b in range(3)]
+    for b, s_ in enumerate(lengths):
+        rows = indices[indptr[b]:indptr[b] + s_]
+        c, sn = torch.cat([cs[s_, :64], cs[s_, :64]]), torch.cat([cs[s_, 64:], cs[s_, 64:]])
+        ob, sb, kb, vb = LO.llama_attn_block_fp32(x[b:b + 1], res[b:b + 1], wqkv, wo, kpool[rows], vpool[rows], g1, 1e-5, c, sn, heads, hd)
+        assert torch.equal(o[b:b + 1], ob) and torch.equal(kn[b:b + 1], kb) and torch.equal(s[b:b + 1], sb)
