@@ -20,4 +20,5 @@ from .api import (  # noqa: F401
 from .checkpoint import convert_state_dict, describe_config, load_decoder  # noqa: F401
 from .decoder import PythiaDecoder, rope_table  # noqa: F401
 from .llama import LlamaLayerStack  # noqa: F401
+from .quality import DecodeQuality, evaluate_decode_quality, step_metrics  # noqa: F401
 from .tp import TPDecoder, shard_cache, shard_dims, shard_head_weights, shard_layer_weights  # noqa: F401

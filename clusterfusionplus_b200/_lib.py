@@ -72,6 +72,7 @@ SIGNATURES = {
     "cf_llama_mlp_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_debug_run_phases": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_int, C.c_void_p]),
     "cf_debug_set_trace": (C.c_int, [C.c_void_p, C.c_int64]),
+    "cf_debug_set_llama_batch_trace": (C.c_int, [C.c_void_p, C.c_int64]),
     "cf_debug_stream_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "cf_pythia_attention_only": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_void_p]),
     "cf_pythia_mlp_only": (C.c_int, [C.c_int] + [C.c_void_p] * 7),

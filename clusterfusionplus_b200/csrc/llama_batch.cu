@@ -28,9 +28,9 @@ struct LbDevice {
     float *qkv32 = nullptr, *records = nullptr;
     unsigned* sync = nullptr;
     int* status = nullptr;
-    CUtensorMap a_y, a_attn;
-    std::map<std::tuple<const void*, int64_t, int64_t>, lb::WMaps> wmaps;
-    std::map<int64_t, CUtensorMap> a_mid;  // by ffn
+    std::map<std::tuple<const void*, int64_t, int64_t, int>, lb::WMaps> wmaps;   // (weights, rows, cols, ranges per CTA)
+    std::map<std::tuple<const void*, int64_t, int>, CUtensorMap> amaps;           // (activations, columns, K blocks per stage)
+    unsigned long long* trace = nullptr;   // diagnostics
 };
 
 constexpr int LB_MAX_DEVICES = 64;
@@ -40,18 +40,15 @@ constexpr int LB_MAX_GRID = 256;
 LbDevice g_lb[LB_MAX_DEVICES];
 std::mutex g_lb_mu;
 
-// fp16 row-major [rows, cols]: box {64 columns, box_rows rows}, 128-byte swizzle
-int encode_sw128(CUtensorMap* tm, const void* ptr, uint64_t cols, uint64_t rows, uint32_t box_rows) {
+// 128-byte-swizzled fp16 tensor map of `rank` dimensions (innermost first; strides in bytes for dimensions 1..)
+int encode_sw128(CUtensorMap* tm, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                 const cuuint32_t* box) {
     CfEncodeTiledFn enc = cf_host_encode_fn();
     if (!enc) return cf_host_fail(CF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return cf_host_fail(CF_ERR_INVALID, "tensor base not 16-byte aligned");
-    if ((cols * 2) % 16 != 0) return cf_host_fail(CF_ERR_INVALID, "row stride not a multiple of 16 bytes");
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {64, box_rows};
-    cuuint32_t es[2] = {1, 1};
-    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(ptr), dims, strides,
+                     box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cf_host_fail(CF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return CF_OK;
@@ -94,8 +91,6 @@ int lb_device(cudaStream_t st, LbDevice** out) {
         d.records = reinterpret_cast<float*>(d.base + o_rec);
         d.sync = reinterpret_cast<unsigned*>(d.base + o_sync);
         d.status = reinterpret_cast<int*>(d.base + o_sync + 16);
-        if ((rc = encode_sw128(&d.a_y, d.y16, LB_H, 16, 16))) return rc;
-        if ((rc = encode_sw128(&d.a_attn, d.attn16, LB_H, 16, 16))) return rc;
         LB_CUDA(cudaFuncSetAttribute(lb::llama_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(lb::smem_bytes())));
         int nb = 0;
@@ -107,17 +102,55 @@ int lb_device(cudaStream_t st, LbDevice** out) {
     return CF_OK;
 }
 
-int weight_maps(LbDevice& d, const void* w, int64_t rows, int64_t cols, lb::WMaps* out) {
-    auto key = std::make_tuple(w, rows, cols);
+// Tensor maps and stage geometry of one weight matrix [rows, cols] whose rows are split over `grid` CTAs in 8-row
+// granules, `ranges` row ranges per CTA (2: the gate / up halves of a merged matrix, rows = rows of one half).
+int weight_maps(LbDevice& d, const void* w, int64_t rows, int64_t cols, int ranges, lb::WMaps* out) {
+    auto key = std::make_tuple(w, rows, cols, ranges);
     auto it = d.wmaps.find(key);
     if (it == d.wmaps.end()) {
         if (d.wmaps.size() >= 4096) d.wmaps.clear();  // maps are host objects: nothing in flight refers to them
         lb::WMaps m;
-        for (int i = 0; i < lb::NBOX; ++i) {
-            int rc = encode_sw128(&m.r[i], w, static_cast<uint64_t>(cols), static_cast<uint64_t>(rows), 8u << i);
+        memset(&m, 0, sizeof(m));
+        const int64_t ng = rows / 8;
+        m.rows_lo = static_cast<int>(ng / d.sm_count) * 8;
+        const int nr_max = ranges * (m.rows_lo + 8);
+        if (nr_max > 256) return cf_host_fail(CF_ERR_UNSUPPORTED, "%d weight rows per CTA (at most 256)", nr_max);
+        const int nkb = static_cast<int>(cols / 64);
+        int kb = 4;
+        while (kb > 1 && (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES || (nkb % kb) != 0)) kb >>= 1;
+        if (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES)
+            return cf_host_fail(CF_ERR_UNSUPPORTED, "a ring stage cannot hold %d weight rows", nr_max);
+        m.kb = kb;
+        m.nset = nr_max <= 128 ? 4 : 2;
+        // {64 K elements, rows, K / 64 blocks}: strides of dimension 1 (a row) and 2 (the next 64 columns)
+        const int64_t all_rows = ranges * rows;
+        cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(all_rows), static_cast<cuuint64_t>(nkb)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+        for (int v = 0; v < 2; ++v) {
+            const int r = m.rows_lo + 8 * v;
+            if (r == 0) continue;  // never used: every CTA then holds rows_lo + 8 rows or none
+            cuuint32_t box[3] = {64, static_cast<cuuint32_t>(r), static_cast<cuuint32_t>(kb)};
+            int rc = encode_sw128(v ? &m.hi : &m.lo, w, 3, dims, strides, box);
             if (rc) return rc;
         }
         it = d.wmaps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return CF_OK;
+}
+
+// K-block-major activations [cols / 64][16][64]: {64, 16 * cols / 64} with box {64, 16 * kb}
+int act_map(LbDevice& d, const void* a, int64_t cols, int kb, CUtensorMap* out) {
+    auto key = std::make_tuple(a, cols, kb);
+    auto it = d.amaps.find(key);
+    if (it == d.amaps.end()) {
+        CUtensorMap m;
+        cuuint64_t dims[2] = {64, static_cast<cuuint64_t>(16 * (cols / 64))};
+        cuuint64_t strides[1] = {128};
+        cuuint32_t box[2] = {64, static_cast<cuuint32_t>(16 * kb)};
+        int rc = encode_sw128(&m, a, 2, dims, strides, box);
+        if (rc) return rc;
+        it = d.amaps.emplace(key, m).first;
     }
     *out = it->second;
     return CF_OK;
@@ -131,8 +164,7 @@ int launch_lb(LbDevice& d, lb::Params& p, cudaStream_t st) {
     p.records = d.records;
     p.sync = d.sync;
     p.status = d.status;
-    p.a_y = d.a_y;
-    p.a_attn = d.a_attn;
+    p.trace = d.trace;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(d.sm_count);
     lc.blockDim = dim3(lb::THREADS);
@@ -170,6 +202,17 @@ int cf_host_lb_probe_status(int dev, int* status) {
 
 extern "C" {
 
+int cf_debug_set_llama_batch_trace(void* device_buffer, int64_t n_slots) {
+    int dev = -1;
+    LB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= LB_MAX_DEVICES) return cf_host_fail(CF_ERR_UNSUPPORTED, "device index %d", dev);
+    if (device_buffer && n_slots < static_cast<int64_t>(LB_MAX_GRID) * 16)
+        return cf_host_fail(CF_ERR_INVALID, "the timeline buffer needs %d slots", LB_MAX_GRID * 16);
+    std::lock_guard<std::mutex> lk(g_lb_mu);
+    g_lb[dev].trace = static_cast<unsigned long long*>(device_buffer);
+    return CF_OK;
+}
+
 int cf_llama_decoder_layer_batch_sglang(void* output, void* residual_output, const void* input, const void* residual,
                                         const void* weight_qkv, const void* weight_o, const int* paged_kv_indptr,
                                         const int* paged_kv_indices, const uint64_t* k_cache_ptrs,
@@ -188,8 +231,10 @@ int cf_llama_decoder_layer_batch_sglang(void* output, void* residual_output, con
     if (rc) return rc;
     lb::Params p;
     memset(&p, 0, sizeof(p));
-    if ((rc = weight_maps(*d, weight_qkv, 3 * LB_H, LB_H, &p.w_qkv))) return rc;
-    if ((rc = weight_maps(*d, weight_o, LB_H, LB_H, &p.w_o))) return rc;
+    if ((rc = weight_maps(*d, weight_qkv, 3 * LB_H, LB_H, 1, &p.w_qkv))) return rc;
+    if ((rc = weight_maps(*d, weight_o, LB_H, LB_H, 1, &p.w_o))) return rc;
+    if ((rc = act_map(*d, d->y16, LB_H, p.w_qkv.kb, &p.a_qkv))) return rc;
+    if ((rc = act_map(*d, d->attn16, LB_H, p.w_o.kb, &p.a_o))) return rc;
     p.mode = lb::MODE_ATTN;
     p.B = static_cast<int>(batch);
     p.H = LB_H;
@@ -227,15 +272,10 @@ int cf_llama_mlp_batch_sglang(const void* input, const void* residual, const voi
     if (rc) return rc;
     lb::Params p;
     memset(&p, 0, sizeof(p));
-    if ((rc = weight_maps(*d, gate_up_weight, 2 * ffn, LB_H, &p.w_gu))) return rc;
-    if ((rc = weight_maps(*d, down_weight, LB_H, ffn, &p.w_down))) return rc;
-    auto it = d->a_mid.find(ffn);
-    if (it == d->a_mid.end()) {
-        CUtensorMap m;
-        if ((rc = encode_sw128(&m, d->mid16, static_cast<uint64_t>(ffn), 16, 16))) return rc;
-        it = d->a_mid.emplace(ffn, m).first;
-    }
-    p.a_mid = it->second;
+    if ((rc = weight_maps(*d, gate_up_weight, ffn, LB_H, 2, &p.w_gu))) return rc;
+    if ((rc = weight_maps(*d, down_weight, LB_H, ffn, 1, &p.w_down))) return rc;
+    if ((rc = act_map(*d, d->y16, LB_H, p.w_gu.kb, &p.a_gu))) return rc;
+    if ((rc = act_map(*d, d->mid16, ffn, p.w_down.kb, &p.a_down))) return rc;
     p.mode = lb::MODE_MLP;
     p.B = static_cast<int>(batch);
     p.H = LB_H;

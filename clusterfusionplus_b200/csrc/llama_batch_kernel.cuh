@@ -8,10 +8,12 @@
 // skinny GEMM  out[b, n] = sum_k act[b, k] * W[n, k]  with b <= 16, and that runs on the 5th
 // generation tensor cores:
 //
-//   * operands: the weight tile (B operand, N = weight rows, K-major, exactly nn.Linear's layout)
-//     and the activation tile (A operand, M = 64 rows of which the first `batch` are real) are both
-//     brought into shared memory by TMA with the 128-byte swizzle; one thread issues
-//     tcgen05.mma.cta_group::1.kind::f16 (M 64, N = 8..128 per box, K 16 per instruction);
+//   * operands: the weight tile (B operand, N = the CTA's weight rows, K-major, exactly nn.Linear's
+//     layout) and the activation tile (A operand, M = 64 rows of which the first `batch` are real) are
+//     both brought into shared memory by TMA with the 128-byte swizzle, one copy each per ring stage; one
+//     thread issues tcgen05.mma.cta_group::1.kind::f16 (M 64, N = the CTA's rows, K 16 per instruction),
+//     alternating between independent accumulator sets so that consecutive K steps do not wait for one
+//     another;
 //   * accumulators live in tensor memory (fp32, lanes = sequences, columns = weight rows) and are read
 //     back once per phase with tcgen05.ld by one warp, which applies the epilogue (store fp32 q/k/v,
 //     silu(gate) * up, fp16 output);
@@ -21,7 +23,7 @@
 // sums have a fixed order and nothing is atomic.  Attention streams each sequence's cached rows
 // through the page table (the pool row of token t of sequence b is indices[indptr[b] + t], one row =
 // one token, as in the reference's `paged_kv_indices[...] * HIDDEN_DIM` addressing, :343-371) with one
-// bulk copy per (row, head), in items of 128 rows spread evenly over the CTAs; partial (max,
+// 256-byte run of asynchronous copies per (row, head), in items of 128 rows spread evenly over the CTAs; partial (max,
 // denominator, numerators) records are merged in a fixed order, the new token is folded in and
 // appended to the pool there.  Phases are separated by grid barriers (bounded waits).
 #pragma once
@@ -40,24 +42,34 @@ constexpr int MAXB = 16;              // sequences per step
 constexpr int D = 128;                // head_dim (include/5090/llama/config.h:1)
 constexpr int NCW = 8;                // consumer warps (attention arithmetic, norms, merge; warp 0 also the GEMM epilogue)
 constexpr int NCT = NCW * 32;
-constexpr int THREADS = NCT + 64;     // + producer warp + MMA warp
+constexpr int NGW = 4;                // warps that gather K/V rows in the attention phase: the TMA warp, the MMA warp, two more
+constexpr int THREADS = NCT + NGW * 32;
 constexpr int NSTAGE = 5;
 constexpr int STAGE_BYTES = 40 * 1024;
 constexpr int A_KB_BYTES = 16 * 128;  // one 64-wide K block of the activation tile: 16 rows x 128 bytes
 constexpr int KV_ROWS = 128;          // cache rows per attention item
 constexpr int REC = D + 4;            // partial record: D numerators, max, denominator, pad
-constexpr int TMEM_COLS = 256;
-constexpr int NBOX = 5;               // weight boxes of 8, 16, 32, 64 and 128 rows
+constexpr int TMEM_COLS = 512;
 
 enum : int { MODE_ATTN = 0, MODE_MLP = 1 };
 
+// One weight matrix [rows, K] as a 3-D tensor {64 K elements, rows, K / 64 blocks}: a box {64, R, kb} brings R
+// rows of kb consecutive 64-wide K blocks in ONE copy, landing block-major ([kb][R][128 bytes], 128-byte swizzle),
+// which is the K-major operand layout the MMA reads.  The rows of a phase are split over the CTAs in 8-row
+// granules, so a CTA holds rows_lo or rows_lo + 8 rows: one map for each.
 struct WMaps {
-    CUtensorMap r[NBOX];  // box {64 K elements, 8 << i rows}, 128-byte swizzle
+    CUtensorMap lo, hi;
+    int rows_lo;  // box rows of `lo`; `hi` has rows_lo + 8
+    int kb;       // K blocks per ring stage (box depth of the maps, and of the matching activation map)
+    int nset;     // accumulator sets the K steps alternate between (independent MMA chains), summed in the epilogue
+    int pad_;
 };
 
 struct alignas(64) Params {
     WMaps w_qkv, w_o, w_gu, w_down;
-    CUtensorMap a_y, a_attn, a_mid;  // activations [16, K] fp16, box {64, 16}, 128-byte swizzle
+    // activations, stored K-block-major [K / 64][16 sequences][64] fp16 so that a stage's tile is one contiguous
+    // copy: 2-D maps {64, 16 * K / 64} with box {64, 16 * kb} for the phase that reads them
+    CUtensorMap a_qkv, a_o, a_gu, a_down;
     int mode, B, H, NH, F;
     float eps;
     const __half *input, *residual, *norm_w;
@@ -69,11 +81,12 @@ struct alignas(64) Params {
     const long long* positions;
     const float* cos_sin;  // [positions, 128]: cos of the 64 rotation angles, then sin
     // scratch
-    __half *y16, *attn16, *mid16;  // [16, H], [16, H], [16, F]
+    __half *y16, *attn16, *mid16;  // K-block-major activations of H, H and F columns (see a_idx)
     float* qkv32;                  // [16, 3H]
     float* records;                // [B * NH + grid][REC]
     unsigned* sync;                // [0] barrier count, [1] exit count
     int* status;
+    unsigned long long* trace;     // diagnostics: [grid][16] nanosecond stamps at the phase boundaries, or nullptr
 };
 
 // ---------------------------------------------------------------- tcgen05 wrappers
@@ -130,6 +143,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
 // N >> 3 in bits [17,23), M >> 4 in bits [24,29).
 __host__ __device__ __forceinline__ uint32_t idesc_f16(int m, int n) {
     return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// element (sequence b, column k) of a K-block-major activation matrix
+__host__ __device__ __forceinline__ size_t a_idx(int b, int k) {
+    return (static_cast<size_t>(k >> 6) * 16 + b) * 64 + (k & 63);
+}
+
+__device__ __forceinline__ void tma3d(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
 }
 
 // 2-D tiled TMA load without cache hint
@@ -212,7 +237,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(smem_u32(full + s), 1);
             mbar_init(smem_u32(empty + s), 1);
-            mbar_init(smem_u32(full2 + s), 1);
+            mbar_init(smem_u32(full2 + s), NGW * 32);  // every lane of the gather warps arrives when its copies have landed
             mbar_init(smem_u32(empty2 + s), NCW);
         }
         mbar_init(smem_u32(acc_bar), 1);
@@ -227,6 +252,12 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+    int trace_ev = 0;
+    auto mark = [&]() {
+        if (p.trace && tid == 0 && trace_ev < 16) p.trace[static_cast<size_t>(cta) * 16 + trace_ev] = globaltimer_ns();
+        ++trace_ev;
+    };
+    mark();
     unsigned bar_epoch = 0;
     // every thread of the CTA calls it; thread 0 counts in and spins (bounded) for the others
     auto grid_barrier = [&]() {
@@ -252,74 +283,64 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
     Ring cr2 = pr2;
     uint32_t acc_phase = 0;
 
-    // ---- one skinny GEMM phase: rows [ra0, ra1) of the weight matrix (and rows [rb0, rb1) of the same
-    // matrix: gate / up pairs) against the activations of all sequences over K columns.  All lanes of
-    // warp 0 call epi(col0, v, u) for every group of 8 accumulator columns of the first range: v = the 8
+    // ---- one skinny GEMM phase: rows [ra0, ra1) of the weight matrix (and, with two = true, the same number
+    // of rows from rb0: gate / up pairs) against the activations of all sequences over K columns.  All lanes
+    // of warp 0 call epi(col0, v, u) for every group of 8 accumulator columns of the first range: v = the 8
     // values of this lane's sequence, u = the same columns of the second range (v again without one).
-    auto row_boxes = [&](int n, int (&sz)[8]) {  // greedy split of n rows (multiple of 8) into boxes
-        int c = 0;
-        for (int i = NBOX - 1; i >= 0; --i)
-            while (n >= (8 << i) && c < 8) {
-                sz[c++] = i;
-                n -= 8 << i;
-            }
-        return c;
-    };
-    auto gemm_phase = [&](const WMaps* wm, const CUtensorMap* am, int K, int ra0, int ra1, int rb0, int rb1, auto epi) {
-        const int na = ra1 - ra0, nb = rb1 - rb0, NR = na + nb;
-        int bxa[8], bxb[8];
-        const int ca = row_boxes(na, bxa), cb = row_boxes(nb, bxb);
-        const int nkb = K / 64;
-        int kb = 4;
-        while (kb > 1 && (kb * (A_KB_BYTES + NR * 128) > STAGE_BYTES || (nkb % kb) != 0)) kb >>= 1;
-        const int nst = nkb / kb;
-        if (NR > 0) {
+    auto gemm_phase = [&](const WMaps* wm, const CUtensorMap* am, int K, int ra0, int ra1, int rb0, bool two, auto epi) {
+        const int na = ra1 - ra0, NR = two ? 2 * na : na;
+        const CUtensorMap* tw = (na == wm->rows_lo) ? &wm->lo : &wm->hi;
+        const int kb = wm->kb, nset = wm->nset, set_stride = TMEM_COLS / nset;
+        const int nst = (K / 64) / kb;
+        // Every CTA needs the same activation tiles; walking K in the same order they would all ask L2 for the
+        // same lines at the same moment.  CTA c starts at stage c * nst / G of the K loop and wraps around, so
+        // the CTAs are spread over the whole activation matrix (the sum order of a row is fixed by its CTA).
+        const int rot = static_cast<int>((static_cast<long long>(cta) * nst) / G);
+        if (na > 0) {
             if (warp == NCW && lane == 0) {
-                // ---- TMA producer
-                for (int st = 0; st < nst; ++st) {
+                // ---- TMA producer: one copy for the activations, one per weight range
+                for (int s0 = 0; s0 < nst; ++s0) {
+                    const int st = (s0 + rot) % nst;
                     mbar_wait(pr.empty + pr.stage * 8, pr.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
                     if (*ab.flag) break;
                     const uint32_t bar = pr.full + pr.stage * 8;
                     const uint32_t sb = pr.base + pr.stage * STAGE_BYTES;
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kb) * (A_KB_BYTES + NR * 128));
-                    for (int j = 0; j < kb; ++j) tma2d(sb + j * A_KB_BYTES, am, (st * kb + j) * 64, 0, bar);
-                    uint32_t wb = sb + kb * A_KB_BYTES;
-                    int row = ra0;
-                    for (int i = 0; i < ca; ++i) {
-                        const int r = 8 << bxa[i];
-                        for (int j = 0; j < kb; ++j) tma2d(wb + j * r * 128, &wm->r[bxa[i]], (st * kb + j) * 64, row, bar);
-                        wb += kb * r * 128;
-                        row += r;
-                    }
-                    row = rb0;
-                    for (int i = 0; i < cb; ++i) {
-                        const int r = 8 << bxb[i];
-                        for (int j = 0; j < kb; ++j) tma2d(wb + j * r * 128, &wm->r[bxb[i]], (st * kb + j) * 64, row, bar);
-                        wb += kb * r * 128;
-                        row += r;
-                    }
+                    tma2d(sb, am, 0, st * kb * 16, bar);
+                    tma3d(sb + kb * A_KB_BYTES, tw, 0, ra0, st * kb, bar);
+                    if (two) tma3d(sb + kb * (A_KB_BYTES + na * 128), tw, 0, rb0, st * kb, bar);
                     pr.advance();
                 }
             } else if (warp == NCW + 1 && lane == 0) {
-                // ---- MMA issuer
-                for (int st = 0; st < nst; ++st) {
+                // ---- MMA issuer.  One thread feeds the tensor core, so the loop body is kept to a few
+                // integer instructions per MMA (with descriptors rebuilt from scratch and a division per
+                // step it measured 130 ns per MMA and bound the whole phase): the descriptors' constant
+                // bits are formed once, per MMA only the 16-byte-unit start address is added.
+                const uint32_t idesc = idesc_f16(64, na);
+                const uint64_t desc_hi = smem_desc_sw128(0);       // everything but the start address
+                const uint32_t setmask = static_cast<uint32_t>(nset - 1);  // nset is 2 or 4
+                const uint32_t a_kb = A_KB_BYTES >> 4, w_kb = static_cast<uint32_t>(na * 128) >> 4;
+                const uint32_t w2 = static_cast<uint32_t>(kb * na * 128) >> 4;  // second weight range
+                for (int s0 = 0; s0 < nst; ++s0) {
                     mbar_wait(cr.full + cr.stage * 8, cr.phase, ab, ST_TIMEOUT_FULL);
                     if (*ab.flag) break;
                     tc_fence_after();
                     const uint32_t sb = cr.base + cr.stage * STAGE_BYTES;
-                    for (int j = 0; j < kb; ++j) {
+                    uint32_t a_lo = sb >> 4, w_lo = (sb + kb * A_KB_BYTES) >> 4;
 #pragma unroll
-                        for (int k16 = 0; k16 < 4; ++k16) {
-                            const uint64_t adesc = smem_desc_sw128(sb + j * A_KB_BYTES + k16 * 32);
-                            const uint32_t accum = (st | j | k16) ? 1u : 0u;
-                            uint32_t wb = sb + kb * A_KB_BYTES;
-                            int col = 0;
-                            for (int i = 0; i < ca + cb; ++i) {
-                                const int r = 8 << (i < ca ? bxa[i] : bxb[i - ca]);
-                                umma_f16(tmem_base + col, adesc, smem_desc_sw128(wb + j * r * 128 + k16 * 32), idesc_f16(64, r), accum);
-                                wb += kb * r * 128;
-                                col += r;
+                    for (int j = 0; j < 4; ++j) {
+                        if (j < kb) {
+#pragma unroll
+                            for (int k16 = 0; k16 < 4; ++k16) {
+                                const uint32_t d0 = tmem_base + (static_cast<uint32_t>(k16) & setmask) * set_stride;
+                                // the first MMA into each set overwrites, all later ones accumulate
+                                const uint32_t accum = (s0 | j | (k16 & ~static_cast<int>(setmask))) ? 1u : 0u;
+                                const uint64_t adesc = desc_hi | (a_lo + 2u * k16);
+                                umma_f16(d0, adesc, desc_hi | (w_lo + 2u * k16), idesc, accum);
+                                if (two) umma_f16(d0 + na, adesc, desc_hi | (w_lo + w2 + 2u * k16), idesc, accum);
                             }
+                            a_lo += a_kb;
+                            w_lo += w_kb;
                         }
                     }
                     umma_commit(cr.empty + cr.stage * 8);  // the stage is free once these MMAs have read it
@@ -328,14 +349,24 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 umma_commit(smem_u32(acc_bar));  // accumulators complete
             }
             if (warp == 0) {
-                // ---- epilogue: thread = sequence (TMEM lane), 8 columns at a time
+                // ---- epilogue: thread = sequence (TMEM lane), 8 columns at a time, the sets added in order
                 mbar_wait(smem_u32(acc_bar), acc_phase, ab, ST_TIMEOUT_FULL);
                 tc_fence_after();
                 if (!*ab.flag) {
                     for (int c0 = 0; c0 < na; c0 += 8) {
                         float v[8], u[8];
                         tmem_ld8(tmem_base + c0, v);
-                        tmem_ld8(tmem_base + (nb > 0 ? na + c0 : c0), u);
+                        tmem_ld8(tmem_base + (two ? na + c0 : c0), u);
+                        for (int q = 1; q < nset; ++q) {
+                            float v2[8], u2[8];
+                            tmem_ld8(tmem_base + q * set_stride + c0, v2);
+                            tmem_ld8(tmem_base + q * set_stride + (two ? na + c0 : c0), u2);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) {
+                                v[k] += v2[k];
+                                u[k] += u2[k];
+                            }
+                        }
                         epi(c0, v, u);
                     }
                 }
@@ -371,7 +402,6 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 *reinterpret_cast<uint4*>(so + v * 8) = o;
             }
             const float rstd = rsqrtf(csum(ss, red, tid) / static_cast<float>(H) + p.eps);
-            __half* y = p.y16 + static_cast<size_t>(cta) * H;
             for (int v = tid; v < H / 8; v += NCT) {
                 // this thread re-reads what it wrote itself
                 const uint4 sr = *reinterpret_cast<const uint4*>(so + v * 8);
@@ -385,13 +415,15 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     const float2 s = __half22float2(s2[k]), g = __half22float2(g2[k]);
                     o2[k] = __floats2half2_rn(s.x * rstd * g.x, s.y * rstd * g.y);
                 }
-                *reinterpret_cast<uint4*>(y + v * 8) = o;
+                *reinterpret_cast<uint4*>(p.y16 + a_idx(cta, v * 8)) = o;
             }
         }
     };
 
     norm_phase();
+    mark();
     grid_barrier();
+    mark();
 
     if (p.mode == MODE_MLP) {
         // ---- gate / up rows in pairs, silu(gate) * up in the epilogue
@@ -400,7 +432,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
             const int g0 = pbegin(cta, NG, G) * 8, g1 = pbegin(cta + 1, NG, G) * 8, ng = g1 - g0;
             __half* mid = p.mid16;
             (void)ng;
-            gemm_phase(&p.w_gu, &p.a_y, H, g0, g1, F + g0, F + g1, [&](int c0, const float (&gv)[8], const float (&uv)[8]) {
+            gemm_phase(&p.w_gu, &p.a_gu, H, g0, g1, F + g0, true, [&](int c0, const float (&gv)[8], const float (&uv)[8]) {
                 uint4 o;
                 __half2* o2 = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -409,15 +441,17 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     const float a1 = gv[2 * k + 1] / (1.f + __expf(-gv[2 * k + 1])) * uv[2 * k + 1];
                     o2[k] = __floats2half2_rn(a0, a1);
                 }
-                if (lane < B) *reinterpret_cast<uint4*>(mid + static_cast<size_t>(lane) * F + g0 + c0) = o;
+                if (lane < B) *reinterpret_cast<uint4*>(mid + a_idx(lane, g0 + c0)) = o;
             });
         }
+        mark();
         grid_barrier();
+        mark();
         {
             const int NG = H / 8;
             const int r0 = pbegin(cta, NG, G) * 8, r1 = pbegin(cta + 1, NG, G) * 8;
             __half* out = p.output;
-            gemm_phase(&p.w_down, &p.a_mid, F, r0, r1, 0, 0, [&](int c0, const float (&v)[8], const float (&)[8]) {
+            gemm_phase(&p.w_down, &p.a_down, F, r0, r1, 0, false, [&](int c0, const float (&v)[8], const float (&)[8]) {
                 uint4 o;
                 __half2* o2 = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -431,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
             const int NG = 3 * H / 8;
             const int r0 = pbegin(cta, NG, G) * 8, r1 = pbegin(cta + 1, NG, G) * 8;
             float* qkv = p.qkv32;
-            gemm_phase(&p.w_qkv, &p.a_y, H, r0, r1, 0, 0, [&](int c0, const float (&v)[8], const float (&)[8]) {
+            gemm_phase(&p.w_qkv, &p.a_qkv, H, r0, r1, 0, false, [&](int c0, const float (&v)[8], const float (&)[8]) {
                 if (lane < B) {
                     float* dst = qkv + static_cast<size_t>(lane) * 3 * H + r0 + c0;
                     *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -439,7 +473,9 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 }
             });
         }
+        mark();
         grid_barrier();
+        mark();
 
         // ---- attention over the cached rows: items (sequence, head, 128-row chunk), evenly split
         if (tid == 0) {
@@ -467,34 +503,51 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
             ch = rem - h * nch;
         };
         const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(D));
-        if (warp == NCW) {
-            // ---- gather producer: the whole warp; lane l copies rows l, l+32, l+64, l+96 of a tile
-            for (int t = ta; t < tb; ++t) {
-                int b, h, ch, s;
+        if (warp >= NCW) {
+            // ---- gather producers: NGW warps, each copies a quarter of a tile's rows with 16-byte asynchronous
+            // copies (one bulk copy per row measured 8 us per item: the copy engine takes one operation at a
+            // time; and one warp alone is bound by its own instruction stream at 4.6 us per item).  Lane l of
+            // gather warp g fetches the pool index of row 32 g + l; the indices of the next item are requested
+            // before the copies of the current one are issued.
+            const int gw = warp - NCW;
+            auto fetch_page = [&](int t, int& b, int& h, int& nvalid) {
+                int ch, s;
                 locate(t, b, h, ch, s);
-                const int row0 = ch * KV_ROWS, nvalid = min(KV_ROWS, s - row0);
-                const int* idx = p.indices + __ldg(p.indptr + b) + row0;
-                int pg[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) pg[i] = (lane + 32 * i < nvalid) ? __ldg(idx + lane + 32 * i) : 0;
+                const int row0 = ch * KV_ROWS;
+                nvalid = min(KV_ROWS, s - row0);
+                const int r = gw * 32 + lane;
+                return (r < nvalid) ? __ldg(p.indices + __ldg(p.indptr + b) + row0 + r) : 0;
+            };
+            int b = 0, h = 0, nvalid = 0, pg = 0;
+            if (ta < tb) pg = fetch_page(ta, b, h, nvalid);
+            for (int t = ta; t < tb; ++t) {
+                int nb = 0, nh = 0, nnv = 0, npg = 0;
+                if (t + 1 < tb) npg = fetch_page(t + 1, nb, nh, nnv);
 #pragma unroll
                 for (int kv = 0; kv < 2; ++kv) {
                     mbar_wait(pr2.empty + pr2.stage * 8, pr2.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
-                    if (*ab.flag) break;
                     const uint32_t bar = pr2.full + pr2.stage * 8;
                     const uint32_t sb = pr2.base + pr2.stage * STAGE_BYTES;
-                    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(nvalid) * D * 2);
-                    __syncwarp();
-                    const __half* pool = kv ? vpool : kpool;
+                    const __half* pool = (kv ? vpool : kpool) + h * D;
+                    // one warp instruction copies two rows: lanes 0-15 the 16-byte pieces of one row, lanes 16-31 of the next
+                    const int hi = lane >> 4, piece = lane & 15;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int r = lane + 32 * i;
-                        if (r < nvalid)
-                            bulk_g2s(sb + r * D * 2, pool + static_cast<size_t>(pg[i]) * H + h * D, D * 2, bar);
+                    for (int i = 0; i < 16; ++i) {
+                        const int rl = 2 * i + hi;                 // row within this warp's quarter
+                        const int page = __shfl_sync(0xffffffffu, pg, rl);
+                        const int r = gw * 32 + rl;
+                        if (r < nvalid) {
+                            const __half* src = pool + static_cast<size_t>(page) * H + piece * 8;
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + r * D * 2 + piece * 16), "l"(src) : "memory");
+                        }
                     }
+                    // counts as this lane's arrival once its copies above are complete
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
                     pr2.advance();
                 }
+                b = nb, h = nh, nvalid = nnv, pg = npg;
             }
+            asm volatile("cp.async.wait_all;" ::: "memory");
         } else if (tid < NCT) {
             // ---- consumers: 16 lanes per row, 8 rows per half-warp and tile, online softmax in fp32
             const int hw = lane >> 4, l16 = lane & 15;
@@ -625,7 +678,9 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
             }
             if (cur_pair >= 0) flush(cur_pair);
         }
+        mark();
         grid_barrier();
+        mark();
 
         // ---- merge: pair (b, h) by CTA (pair % G): fold in the new token, append it to the pool
         if (tid < NCT) {
@@ -674,18 +729,20 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                             den = fmaf(w, __ldcg(rec + D + 1), den);
                         }
                     }
-                    p.attn16[static_cast<size_t>(b) * H + h * D + tid] = __float2half_rn(num / den);
+                    p.attn16[a_idx(b, h * D + tid)] = __float2half_rn(num / den);
                 }
             }
         }
+        mark();
         grid_barrier();
+        mark();
 
         // ---- output projection
         {
             const int NG = H / 8;
             const int r0 = pbegin(cta, NG, G) * 8, r1 = pbegin(cta + 1, NG, G) * 8;
             __half* out = p.output;
-            gemm_phase(&p.w_o, &p.a_attn, H, r0, r1, 0, 0, [&](int c0, const float (&v)[8], const float (&)[8]) {
+            gemm_phase(&p.w_o, &p.a_o, H, r0, r1, 0, false, [&](int c0, const float (&v)[8], const float (&)[8]) {
                 uint4 o;
                 __half2* o2 = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -698,6 +755,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
     // ---- leave: tensor memory back, exit count, the last CTA re-arms the barrier words
     tc_fence_before();
     __syncthreads();
+    mark();
     if (warp == NCW + 1) tmem_dealloc(tmem_base, TMEM_COLS);
     if (tid == 0) {
         __threadfence();

@@ -185,6 +185,11 @@ int cf_llama_mlp_batch_sglang(const void* input, const void* residual, const voi
                               const void* rms_weight, float eps, int64_t ffn, int64_t batch, void* output,
                               void* residual_out, void* stream);
 
+/* Diagnostic: while a buffer is set (uint64 [256][16] or larger), every batched Llama launch on the current device
+ * stamps the nanosecond timer of each CTA at its phase boundaries (start, after the norm, after each grid barrier and
+ * each phase, end).  NULL switches it off.  No counterpart in the reference. */
+int cf_debug_set_llama_batch_trace(void* device_buffer, int64_t n_slots);
+
 /* Diagnostic: run any subset of the layer's phases (bit 0: LayerNorm + QKV + MLP-up,
  * bit 1: RoPE + KV append + attention, bit 2: O-proj + MLP-down + residual) in one
  * launch, reading what earlier phases left in the library's scratch.  Used by the

@@ -50,3 +50,26 @@ def test_unsupported_variants_are_refused():
         cf.describe_config(GPTNeoXConfig(**base, hidden_act="relu"))
     with pytest.raises(RuntimeError):
         cf.describe_config(GPTNeoXConfig(**base, layer_norm_eps=1e-6))
+
+
+def test_quality_metric_definitions():
+    """step_metrics / DecodeQuality on hand-made logits: the definitions of the reference's report
+    (tests/evaluate_decode_quality.py:74-79, 161-199)."""
+    import math
+    from clusterfusionplus_b200.quality import DecodeQuality, kl_divergence, step_metrics
+    ref = torch.arange(20, dtype=torch.float32)            # arg-max 19, top-5 = {15..19}
+    same = ref.clone()
+    m = step_metrics(ref, same, torch.ones(4), torch.ones(4))
+    assert m == {"token_match": 1.0, "logits_mae": 0.0, "top5_agree": 1.0, "top10_agree": 1.0, "kl_divergence": 0.0,
+                 "hidden_mae": 0.0}
+    other = ref.clone()
+    other[19], other[18] = ref[18], ref[19]               # swap the two best: token differs, the SETS agree
+    m = step_metrics(ref, other)
+    assert m["token_match"] == 0.0 and m["top5_agree"] == 1.0 and m["top10_agree"] == 1.0
+    assert abs(m["logits_mae"] - 2.0 / 20) < 1e-7
+    p, q = torch.tensor([0.0, math.log(3.0)]), torch.tensor([0.0, 0.0])   # p = (1/4, 3/4), q = (1/2, 1/2)
+    assert abs(kl_divergence(p, q) - (0.25 * math.log(0.5) + 0.75 * math.log(1.5))) < 1e-6
+    dq = DecodeQuality()
+    dq.add(ref, same), dq.add(ref, other)
+    s = dq.summary()
+    assert s["total_tokens"] == 2 and s["token_match_rate"] == 50.0 and s["top5_agreement"] == 100.0

@@ -60,3 +60,32 @@ def test_prefill_fills_the_caches_like_token_by_token_decode():
     assert int(a.seq_len.item()) == m and int(a.token.item()) == prompt[-1]
     a.close()
     b.close()
+
+
+def test_decode_quality_metrics_against_huggingface():
+    """The reference's decode-quality report (tests/evaluate_decode_quality.py:131-199: token match, logits MAE,
+    top-5 / top-10 agreement, KL divergence, teacher forced) between HuggingFace in fp32 and the fused decoder,
+    on a random-init model of the architecture (no checkpoint is available offline)."""
+    import clusterfusionplus_b200 as cf
+    cfg, model = tiny_neox("gelu", seed=3)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 11), generator=torch.Generator().manual_seed(9))
+    n_new = 32
+    state = {}
+    with torch.no_grad():
+        out = model(prompt[:, :-1], use_cache=True)
+        state["past"] = out.past_key_values
+
+    def hf_step(token):
+        with torch.no_grad():
+            o = model(torch.tensor([[token]]), past_key_values=state["past"], use_cache=True, output_hidden_states=True)
+        state["past"] = o.past_key_values
+        return o.logits[0, -1], None
+
+    dec = cf.load_decoder(model.state_dict(), cfg, max_seq=64, device="cuda:0", use_graph=False)
+    dec.prefill(prompt[0].tolist())
+    rep = cf.evaluate_decode_quality(dec, hf_step, int(prompt[0, -1]), n_new)
+    assert rep["total_tokens"] == n_new
+    assert rep["token_match_rate"] == 100.0 and rep["top5_agreement"] >= 95.0, rep
+    assert rep["logits_mae"] <= 2e-3 and rep["kl_divergence"] <= 1e-5, rep
+    assert cf.device_status() == 0
+    dec.close()
