@@ -427,6 +427,85 @@ def run_ours(args, rank, world):
         raise SystemExit(f"tensor-parallel parity check failed: {json.dumps(parity)}")
 
 
+def run_graph_step_api(args):
+    """What a caller of the reference's own API gets (`--api graph_step`): the decode loop of the reference's
+    tests/benchmark_decode_6b9.py:133-198 -- embedding lookup, one pythia_6b9_graph_decode_step per layer through
+    per-layer graph contexts, torch final LayerNorm + LM head + arg-max -- with token id and sequence length kept
+    on the device (graph_set_device_state) and the whole token captured once in a CUDA graph.  Same workload,
+    metric and roofline arithmetic as the default line, which runs the whole token as ONE launch instead."""
+    import clusterfusionplus_b200 as cf
+    import torch.nn.functional as F
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    H, NH, D, R, Fd, V = SHAPES[args.model]
+    pre = f"pythia_{args.model}_"
+    create, step, destroy, set_state = (getattr(cf, pre + n) for n in
+                                        ("create_graph_context", "graph_decode_step", "destroy_graph_context", "graph_set_device_state"))
+    layers, head, caches, max_seq = build_model(args, dev)
+    cos_t, sin_t = cf.rope_table(max_seq, R, dev)
+    seq = torch.full((1,), args.ctx, dtype=torch.int32, device=dev)
+    token = torch.full((1,), 17, dtype=torch.int64, device=dev)
+    for l, (w, (k, v)) in enumerate(zip(layers, caches)):
+        create(l, k, v, w["qkv_weight"], w["o_weight"], w["mlp_up_weight"], w["mlp_down_weight"], max_seq)
+        set_state(l, seq, cos_t, sin_t)
+
+    def one_token():
+        h = head["embed_in"].index_select(0, token).contiguous()
+        for l, (w, (k, v)) in enumerate(zip(layers, caches)):
+            h, _, _ = step(l, h, w["ln_weight"], w["ln_bias"], w["qkv_bias"], w["o_bias"], cos_t[0], sin_t[0], k, v,
+                           w["post_ln_weight"], w["post_ln_bias"], w["mlp_up_bias"], w["mlp_down_bias"], 0)
+        h = F.layer_norm(h, (H,), head["final_ln_weight"], head["final_ln_bias"], eps=1e-5)
+        logits = h @ head["embed_out"].t()
+        token.copy_(torch.argmax(logits, dim=-1))
+        seq.add_(1)
+
+    K, W = args.steps, args.warmup
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        one_token()  # descriptor uploads happen here, outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_token()
+    seq.fill_(args.ctx)
+    token.fill_(17)
+    for _ in range(W):
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(K):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.summary(t0, time.perf_counter())
+    us = e0.elapsed_time(e1) / K * 1e3
+    status = cf.device_status()
+    peak, peak_src = hbm_peak()
+    bytes_token = algorithmic_bytes_per_token(args.model, args.layers, args.ctx + W + K / 2)
+    achieved = bytes_token / (us * 1e-6) / 1e9
+    cfg = workload_config(args, 1)
+    cfg["workload"] += f"; driven through the reference API: {args.layers} x graph_decode_step + torch embedding / final LayerNorm / LM head / arg-max per token"
+    print(json.dumps({
+        "metric": METRIC if (args.model == "6b9" and args.ctx == 4096) else f"Pythia-{args.model} B=1 decode TPOT (us) at {args.ctx} context",
+        "value": us, "unit": "us/token", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": us / 1e3,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
+        "data": "synthetic", "config": cfg, "clocks": clocks, "gpu_launches": K * args.layers,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "bytes_per_launch_algorithmic": bytes_token / args.layers,
+                     "frac_of_8TBs_nominal": achieved / 8000.0,
+                     "kernel": "fused_decode_kernel, one launch per layer (+ torch library kernels for the tail)"},
+        "device_status": status,
+    }), flush=True)
+    for l in range(len(layers)):
+        destroy(l)
+
+
 def tensor_peak():
     """(TFLOP/s, source): the measured cuBLAS bf16 burst figure of this pool if the driver left one."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -662,6 +741,9 @@ def main():
     ap.add_argument("--llama-ctx", type=int, default=0,
                     help="instead of Pythia decode: one step through a Llama-2-7B-shaped layer stack with this many "
                          "cached rows per layer (1 GPU, batch 1; a secondary line)")
+    ap.add_argument("--api", default="decoder", choices=["decoder", "graph_step"],
+                    help="decoder: the whole token as one launch (default); graph_step: the reference's per-layer "
+                         "graph_decode_step API in the reference's decode loop, captured in a CUDA graph (1 GPU)")
     ap.add_argument("--batch", type=int, default=1,
                     help="with --llama-ctx: decode sequences per step; > 1 (or --llama-batched) uses the batched, paged blocks")
     ap.add_argument("--llama-batched", action="store_true", help="with --llama-ctx: the batched, paged blocks even at batch 1")
@@ -682,6 +764,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.api == "graph_step":
+        if rank == 0:
+            run_graph_step_api(args)
         return
     if world != args.gpus:
         if world == 1 and args.gpus > 1:

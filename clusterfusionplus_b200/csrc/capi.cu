@@ -104,10 +104,12 @@ int encode_2d(CUtensorMap* tm, const void* ptr, uint64_t inner, uint64_t outer, 
     return CF_OK;
 }
 
-// contiguous row-major weight [rows, cols]: boxes of 8, 32 and 64 rows x 256 columns
+// contiguous row-major weight [rows, cols]: boxes of 8, 16, 24, 32 and 64 rows x 256 columns
 int encode_weight(WeightMaps* m, const void* ptr, uint64_t cols, uint64_t rows) {
     int rc;
     if ((rc = encode_2d(&m->r8, ptr, cols, rows, cols, KCHUNK, GRAN))) return rc;
+    if ((rc = encode_2d(&m->r16, ptr, cols, rows, cols, KCHUNK, 2 * GRAN))) return rc;
+    if ((rc = encode_2d(&m->r24, ptr, cols, rows, cols, KCHUNK, 3 * GRAN))) return rc;
     if ((rc = encode_2d(&m->r32, ptr, cols, rows, cols, KCHUNK, 4 * GRAN))) return rc;
     return encode_2d(&m->r64, ptr, cols, rows, cols, KCHUNK, 8 * GRAN);
 }

@@ -86,10 +86,11 @@ enum : int {
 };
 
 // Per-layer descriptor, resident in device memory.
-// A weight matrix is described three times, with boxes of 8, 32 and 64 rows (x 256 K elements):
-// a stage's run of consecutive granules is fetched with the fewest TMA operations.
+// A weight matrix is described five times, with boxes of 8, 16, 24, 32 and 64 rows (x 256 K elements):
+// a stage's run of up to 9 consecutive granules is fetched with at most two TMA operations (the copy engine
+// takes them one at a time, a fraction of a microsecond each, so their number matters as much as their bytes).
 struct WeightMaps {
-    CUtensorMap r8, r32, r64;
+    CUtensorMap r8, r16, r24, r32, r64;
 };
 
 struct alignas(128) LayerDesc {
@@ -262,6 +263,34 @@ __host__ __device__ __forceinline__ int part_of(int t, int total, int parts) {
 }
 __host__ __device__ __forceinline__ int head_owner(int h, int NH, int G) { return part_begin(h, G, NH); }
 
+// How a row-partitioned GEMV phase of `cnt` 8-row granules over `KC` K chunks is cut into ring stages.
+// A stage has NSLOT slots of (granule, chunk).  With many granules a stage is up to NSLOT granules of ONE
+// chunk (m = 1).  With few granules per CTA (small models, tensor-parallel shards) such stages would be
+// mostly empty and the phase would be bound by the number of stages, not by bytes; a stage then takes
+// n <= 4 granules of m = NSLOT / n consecutive chunks, and the chunk partials of a row are added at the
+// end of the round.  Picks the n with the fewest stages (ties: the larger n); returns m, sets n.
+__host__ __device__ __forceinline__ int plan_rounds(int cnt, int KC, int& n) {
+    n = NSLOT;
+    // only where ONE stage per chunk would leave slots empty; with more granules the remainder round of a
+    // multi-chunk plan is nearly empty and the plan measured slower (2 GPUs: 1.63 -> 2.12 ms per token)
+    if (cnt <= 0 || cnt >= NSLOT) return 1;
+    // one chunk per stage unless the alternative needs at most half of the stages: every round of the
+    // alternative ends with a reduction between the warps, and at three quarters (6 granules, 4 GPUs) it
+    // measured slower (1.15 -> 1.24 ms per token) while at three eighths (3 granules, 8 GPUs) it is faster
+    // (1.08 -> 1.01 ms)
+    int best = (ceil_div(cnt, NSLOT) * KC) / 2 + 1, m = 1;
+    for (int cand = 4; cand >= 1; --cand) {
+        const int mm = NSLOT / cand;
+        const int stages = ceil_div(cnt, cand) * ceil_div(KC, mm);
+        if (stages < best) {
+            best = stages;
+            n = cand;
+            m = mm;
+        }
+    }
+    return m;
+}
+
 // ring cursor: same arithmetic on the producer and the consumer side
 struct Cursor {
     int stage;
@@ -283,6 +312,7 @@ struct Smem {
     float* pl;      // WTS_SLOTS their denominators
     int* offs;      // WTS_SLOTS their offsets in the partial buffer (-1: none), fixed for a launch
     float* recv;    // MAX_P3_ROWS
+    float* rsum;    // NSLOT * GRAN
     uint64_t* full;
     uint64_t* empty;
     uint64_t* xbar;
@@ -298,7 +328,7 @@ struct Smem {
 
 __host__ __device__ __forceinline__ size_t smem_bytes_for(int nstage, int xbuf_floats) {
     return static_cast<size_t>(nstage) * STAGE_BYTES + static_cast<size_t>(xbuf_floats) * 4 +
-           (64 + 3 * WTS_SLOTS + MAX_P3_ROWS) * 4 + (2 * MAX_STAGES + 9) * 8 + 16;
+           (64 + 3 * WTS_SLOTS + MAX_P3_ROWS + NSLOT * GRAN) * 4 + (2 * MAX_STAGES + 9) * 8 + 16;
 }
 
 __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats) {
@@ -310,7 +340,8 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
     s.pl = s.pm + WTS_SLOTS;
     s.offs = reinterpret_cast<int*>(s.pl + WTS_SLOTS);
     s.recv = reinterpret_cast<float*>(s.offs + WTS_SLOTS);
-    s.full = reinterpret_cast<uint64_t*>(s.recv + MAX_P3_ROWS);
+    s.rsum = s.recv + MAX_P3_ROWS;
+    s.full = reinterpret_cast<uint64_t*>(s.rsum + NSLOT * GRAN);
     s.empty = s.full + MAX_STAGES;
     s.xbar = s.empty + MAX_STAGES;
     s.h_go = s.xbar + 1;
@@ -739,7 +770,9 @@ struct Producer {
         int w = 0;
         for (; w + 8 <= n; w += 8) tile(dst + w * SLOT_BYTES, &tm->r64, kx, (g0 + w) * GRAN, bar);
         for (; w + 4 <= n; w += 4) tile(dst + w * SLOT_BYTES, &tm->r32, kx, (g0 + w) * GRAN, bar);
-        for (; w < n; ++w) tile(dst + w * SLOT_BYTES, &tm->r8, kx, (g0 + w) * GRAN, bar);
+        if (n - w == 3) tile(dst + w * SLOT_BYTES, &tm->r24, kx, (g0 + w) * GRAN, bar);
+        else if (n - w == 2) tile(dst + w * SLOT_BYTES, &tm->r16, kx, (g0 + w) * GRAN, bar);
+        else if (n - w == 1) tile(dst + w * SLOT_BYTES, &tm->r8, kx, (g0 + w) * GRAN, bar);
     }
     // one stage of `n` row granules (rows g0*8 ...) at K offset kx
     __device__ __forceinline__ void rows_stage(const WeightMaps* tm, int kx, int g0, int n) {
@@ -768,6 +801,31 @@ struct Producer {
                                                 int cntB, int KC) {
         const int cnt = cntA + cntB;
         if (cnt <= 0) return;
+        int np;
+        const int m = plan_rounds(cnt, KC, np);
+        if (m > 1) {
+            // few granules: stages of np granules x up to m chunks (slot = chunk * n + granule)
+            for (int g = 0; g < cnt; g += np) {
+                const int n = min(np, cnt - g);
+                const int nA = max(0, min(cntA - g, n));
+                for (int c0 = 0; c0 < KC; c0 += m) {
+                    const int mt = min(m, KC - c0);
+                    if (stop()) return;
+                    acquire();
+                    if (*ab.flag) return;
+                    const uint32_t bar = full_addr + cur.stage * 8;
+                    expect(bar, static_cast<uint32_t>(n * mt) * SLOT_BYTES);
+                    const uint32_t dst = ring_addr + cur.stage * STAGE_BYTES;
+                    for (int cc = 0; cc < mt; ++cc) {
+                        const uint32_t d = dst + cc * n * SLOT_BYTES;
+                        if (nA > 0) issue_run(tmA, (c0 + cc) * KCHUNK, gA0 + g, nA, d, bar);
+                        if (n > nA) issue_run(tmB, (c0 + cc) * KCHUNK, gB0 + g + nA - cntA, n - nA, d + nA * SLOT_BYTES, bar);
+                    }
+                    stage_done();
+                }
+            }
+            return;
+        }
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = 0;
         for (int r = 0; r < nr; ++r) {
@@ -813,6 +871,7 @@ struct Consumer {
     AbortCtl ab;
     int warp, lane;
     bool touch_only;
+    float* rsum;  // shared memory, NSLOT x GRAN floats: per-slot row sums of a multi-chunk round
 
     __device__ __forceinline__ const uint8_t* wait_stage() {
         mbar_wait(full_addr + cur.stage * 8, cur.phase, ab, ST_TIMEOUT_FULL);
@@ -872,6 +931,52 @@ struct Consumer {
             a_done = true;
         }
         if (cnt <= 0) return;
+        int np;
+        const int m = plan_rounds(cnt, KC, np);
+        if (m > 1) {
+            // mirror of the producer's multi-chunk stages; the chunk partials of a row meet in rsum
+            const int tid = warp * 32 + lane;
+            for (int g = 0; g < cnt; g += np) {
+                const int n = min(np, cnt - g);
+                const int gi0 = warp % n, cc0 = warp / n, gi1 = (warp + NCWARP) % n, cc1 = (warp + NCWARP) / n;
+                const float* x0 = (g + gi0 < cntA) ? xsA : xsB;
+                const float* x1 = (g + gi1 < cntA) ? xsA : xsB;
+                float acc0[GRAN], acc1[GRAN];
+#pragma unroll
+                for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
+                for (int c0 = 0; c0 < KC; c0 += m) {
+                    const int mt = min(m, KC - c0);
+                    const uint8_t* st = wait_stage();
+                    if (!touch_only) {
+                        if (warp < n * mt) gemv_slot(st + warp * SLOT_BYTES, x0 + (c0 + cc0) * KCHUNK, lane, acc0);
+                        if (warp + NCWARP < n * mt) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, x1 + (c0 + cc1) * KCHUNK, lane, acc1);
+                    }
+                    release_stage();
+                }
+                if (warp < n * m) {
+                    const float v = warp_reduce8(acc0, lane);
+                    if ((lane & 3) == 0) rsum[warp * GRAN + reduce8_row(lane)] = v;
+                }
+                if (warp + NCWARP < n * m) {
+                    const float v = warp_reduce8(acc1, lane);
+                    if ((lane & 3) == 0) rsum[(warp + NCWARP) * GRAN + reduce8_row(lane)] = v;
+                }
+                consumer_sync(NCTHR);
+                if (tid < n * GRAN) {
+                    const int gi = tid / GRAN, r = tid - gi * GRAN;
+                    float v = 0.f;
+                    for (int cc = 0; cc < m; ++cc) v += rsum[(cc * n + gi) * GRAN + r];  // chunk order: fixed
+                    if (g + gi < cntA) epiA(g + gi, r, v);
+                    else epiB(g + gi - cntA, r, v);
+                }
+                consumer_sync(NCTHR);  // rsum is rewritten by the next round
+                if (!a_done && g + n >= cntA) {
+                    after_a();
+                    a_done = true;
+                }
+            }
+            return;
+        }
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = 0;
         for (int r = 0; r < nr; ++r) {
@@ -885,8 +990,10 @@ struct Consumer {
             for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
             for (int c = 0; c < KC; ++c) {
                 const uint8_t* st = wait_stage();
-                if (a0) gemv_slot(st + warp * SLOT_BYTES, x0 + c * KCHUNK, lane, acc0);
-                if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, x1 + c * KCHUNK, lane, acc1);
+                if (!touch_only) {
+                    if (a0) gemv_slot(st + warp * SLOT_BYTES, x0 + c * KCHUNK, lane, acc0);
+                    if (a1) gemv_slot(st + (warp + NCWARP) * SLOT_BYTES, x1 + c * KCHUNK, lane, acc1);
+                }
                 release_stage();
             }
             if (a0) {
@@ -1108,7 +1215,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     trace_mark(p, cta, l, TR_PROD_P3);
                 }
             }
-            if (p.phase_mask & PH_P4) pr.rows_phase(&p.tail->tm_head, g4a, g4b - g4a, KC1);
+            // (the LM head as the second matrix of a two-matrix phase whose first matrix is empty)
+            if (p.phase_mask & PH_P4) pr.rows_phase2(&p.tail->tm_head, 0, 0, &p.tail->tm_head, g4a, g4b - g4a, KC1);
             // After an abort the consumers stop draining the ring: give the copies
             // already issued a bounded chance to land before this CTA's shared
             // memory goes away.
@@ -1459,6 +1567,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         co.warp = warp;
         co.lane = lane;
         co.touch_only = p.touch_only != 0;
+        co.rsum = sm.rsum;
         unsigned epoch = 0;
         uint32_t xparity = 0, hparity = 0, mparity = 0, qpar0 = 0, qpar1 = 0;
         unsigned nflush = 0;  // attention partials handed to the helper warps so far (all layers)
@@ -1870,16 +1979,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (tid == 0) trace_mark(p, cta, p.n_layers, TR_LN_DONE);
                 const int row0 = g4a * GRAN, V = Tl->vocab;
                 float* lg = p.logits;
-                co.rows_phase(g4b - g4a, KC1, sm.xbuf, [&](int g, int r, float v) {
-                    const int row = row0 + g * GRAN + r;
-                    if (row < V) {
-                        if (lg) lg[row] = v;
-                        if (v > best || (v == best && row < best_i)) {
-                            best = v;
-                            best_i = row;
+                co.rows_phase2(
+                    0, g4b - g4a, KC1, sm.xbuf, sm.xbuf, [](int, int, float) {},
+                    [&](int g, int r, float v) {
+                        const int row = row0 + g * GRAN + r;
+                        if (row < V) {
+                            if (lg) lg[row] = v;
+                            if (v > best || (v == best && row < best_i)) {
+                                best = v;
+                                best_i = row;
+                            }
                         }
-                    }
-                });
+                    },
+                    [] {});
             }
             if (tid == 0) trace_mark(p, cta, p.n_layers, TR_P1_DONE);
             // arg-max: warp, then CTA, then (after a grid barrier) CTA 0
