@@ -42,8 +42,8 @@ SHAPES = {  # hidden, heads, head_dim, rotary, ffn, vocab
 
 # DRAM traffic of ONE whole-token launch (6.9B, 4096 cached rows): dram__bytes_read.sum +
 # dram__bytes_write.sum of ncu captures of 2- and 4-layer models of the same shapes, scaled to 32
-# layers (traffic is linear in the layer count): 417.9 MB for the tail + 32 x 472.9 MB per layer.
-NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = 15.551e9
+# layers (traffic is linear in the layer count): 415.4 MB for the tail + 32 x 470.6 MB per layer.
+NCU_TRAFFIC_BYTES_PER_TOKEN_6B9_4K = 15.475e9
 
 
 def algorithmic_bytes_per_token(model: str, n_layers: int, ctx: float, tp: int = 1) -> float:
@@ -282,6 +282,45 @@ def tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp
     return out
 
 
+def phase_timeline(cf, dec, args, n_layers, barrier):
+    """Device timeline of one token (`--timeline`): one eager launch with the kernel's phase stamps switched on
+    (cf_debug_set_trace: globaltimer written by thread 0 of every CTA at each phase boundary).  Returns, in us since
+    the layer's first CTA started and averaged over layers 1..n-1, min / mean / max over the CTAs of: LayerNorm done,
+    P1 rows done, P2 entered, P2 done, P3 entered, P3 operands staged, P3 GEMV done, P3 done (exchange over);
+    the mean distance between layer starts and the length of the token's tail (final LayerNorm, LM head, arg-max)."""
+    import numpy as np
+    from clusterfusionplus_b200 import _lib
+    NE = 16
+    G = cf.launch_info(cf.CF_PYTHIA_6B9 if args.model == "6b9" else cf.CF_PYTHIA_2B8)["grid"]
+    dec.use_graph = False
+    dec.reset(args.ctx, 17)
+    for _ in range(3):
+        dec.step()
+    barrier()
+    tr = torch.zeros(G * (n_layers + 1) * NE, dtype=torch.int64, device=dec.token.device)
+    _lib.check(_lib.lib.cf_debug_set_trace(tr.data_ptr(), tr.numel()))
+    dec.step()
+    torch.cuda.synchronize()
+    _lib.check(_lib.lib.cf_debug_set_trace(None, 0))
+    barrier()
+    dec.use_graph = True
+    t = tr.cpu().numpy().reshape(G, n_layers + 1, NE).astype(np.float64)
+    names = ["layernorm_done", "p1_done", "p2_entered", "p2_done", "p3_entered", "p3_staged", "p3_gemv_done", "p3_done"]
+    acc = np.zeros((len(names), 3))
+    for l in range(1, n_layers):
+        base = t[:, l, 0].min()
+        for e in range(len(names)):
+            v = (t[:, l, e + 1] - base) / 1e3
+            acc[e] += (v.min(), v.mean(), v.max())
+    acc /= max(1, n_layers - 1)
+    starts = np.array([(t[:, l, 0].min() - t[:, 0, 0].min()) / 1e3 for l in range(n_layers)])
+    tail = t[:, n_layers, :]
+    return {"unit": "us since the layer's first CTA started; [min, mean, max] over CTAs, mean over layers 1..n-1",
+            "events": {n: [round(float(x), 2) for x in acc[i]] for i, n in enumerate(names)},
+            "layer_pitch_us": round(float(np.diff(starts).mean()), 2) if n_layers > 1 else None,
+            "tail_us": round(float((tail[:, 3].max() - tail[:, 0].min()) / 1e3), 2)}
+
+
 def run_ours(args, rank, world):
     import torch.distributed as dist
     import clusterfusionplus_b200 as cf
@@ -371,6 +410,7 @@ def run_ours(args, rank, world):
     parity = None
     if tp > 1 and not args.no_parity:
         parity = tp_parity(cf, dist, args, dec, dims, layers, head, caches, max_seq, rank, tp, dev)
+    timeline = phase_timeline(cf, dec, args, args.layers, barrier) if args.timeline else None
     if rank != 0:
         dec.close()
         if tp > 1:
@@ -405,6 +445,8 @@ def run_ours(args, rank, world):
         "launch": cf.launch_info(cf.CF_PYTHIA_6B9 if args.model == "6b9" else cf.CF_PYTHIA_2B8),
         "device_status": status,
     }
+    if timeline is not None:
+        line["timeline"] = timeline
     if tp == 1 and not args.no_read_ceiling:
         with_math, touch = read_ceiling_gbs(dev, H)
         line["roofline"]["read_ceiling_gbs"] = with_math
@@ -736,6 +778,8 @@ def main():
                     help="skip the measurement of the kernel's own read-streaming ceiling (N = 1)")
     ap.add_argument("--no-parity", action="store_true",
                     help="N > 1: skip the comparison with a single-GPU decode of the same model (outside the timed regions)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add the device timeline of one token (phase stamps of every CTA, rank 0's view) to the line")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N > 1: in-kernel all-reduce over peer memory (default) or one NCCL all-reduce per layer")
     ap.add_argument("--llama-ctx", type=int, default=0,

@@ -9,7 +9,7 @@ this package fails if that library has not been built.
 """
 from ._lib import CF_PYTHIA_2B8, CF_PYTHIA_6B9, CfDims, LIB_PATH  # noqa: F401
 from .api import (  # noqa: F401
-    device_status, launch_info, llama_decoder_layer_batch_decode_sglang, llama_decoder_layer_sglang,
+    device_status, launch_info, llama_decoder_layer, llama_decoder_layer_batch_decode_sglang, llama_decoder_layer_sglang,
     llama_mlp_batch_sglang, llama_mlp_sglang, model_dims,
     pythia_2b8_attention_only, pythia_2b8_create_graph_context, pythia_2b8_decoder_layer,
     pythia_2b8_decoder_layer_split, pythia_2b8_destroy_graph_context, pythia_2b8_graph_decode_step,

@@ -166,6 +166,17 @@ def pythia_2b8_mlp_only(input, attn_output, mlp_intermediate, mlp_down_weight, m
     return out
 
 
+def llama_decoder_layer(input, weight_qkv, weight_o, k_cache, v_cache, rms_input_weight, cos, sin):
+    """Refused: the reference's first Llama entry point (include/pybind.cpp:66-74,
+    include/5090/llama/llama_kernel_dispatch.cu:4-120) takes the projection weights TRANSPOSED (its caller,
+    chat/llama/model.py:316-323, stacks wq.T, wk.T, wv.T and passes wo.T), a layout that exists for that
+    kernel's TMA boxes.  The same block over weights in nn.Linear layout is llama_decoder_layer_sglang; a
+    second set of tensor maps for the transposed layout is not built."""
+    raise NotImplementedError(
+        "llama_decoder_layer (transposed weights) is not provided; call llama_decoder_layer_sglang with the q/k/v and "
+        "output projection weights in nn.Linear layout [out, in] (transpose each block back once, outside the decode loop)")
+
+
 def llama_decoder_layer_sglang(input, residual, weight_qkv, weight_o, k_cache, v_cache, rms_input_weight, eps, cos, sin):
     """(output[1,4096], residual[1,4096], k_new[1,32,128], v_new[1,32,128]) of the Llama-2-7B attention block.
     `residual` is updated in place to input + residual (fused add + RMSNorm convention) and returned; the

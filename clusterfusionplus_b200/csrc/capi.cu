@@ -402,6 +402,10 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     const void* fn = kernel_ptr(d.head_dim, c.cs);
     p.qkv_any_epoch = (p.phase_mask & PH_P1) ? 0 : 1;
     p.part_any_epoch = (p.phase_mask & PH_P2) ? 0 : 1;
+    // CFB200_PDL=1: per-layer launches (never the whole-token decoder, whose predecessor writes the token and the
+    // sequence length) are chained by programmatic dependent launch
+    p.pdl = (env_int("CFB200_PDL", 0) != 0 && !(p.phase_mask & PH_P4) && p.tp_size <= 1) ? 1 : 0;
+    p.merge_seg_max = env_int("CFB200_MERGE_SEG", 0);
     p.trace = nullptr;
     if (ds.trace && static_cast<size_t>(c.grid) * (p.n_layers + 1) * TRACE_EVENTS <= ds.trace_slots) p.trace = ds.trace;
     for (int attempt = 0; attempt < 2; ++attempt) {
@@ -410,7 +414,7 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         lc.blockDim = dim3(NTHREADS);
         lc.dynamicSmemBytes = smem;
         lc.stream = st;
-        cudaLaunchAttribute at[2];
+        cudaLaunchAttribute at[3];
         int na = 0;
         if (c.cs > 1) {
             at[na].id = cudaLaunchAttributeClusterDimension;
@@ -419,7 +423,13 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
             at[na].val.clusterDim.z = 1;
             ++na;
         }
-        if (c.coop) {
+        if (p.pdl) {
+            // may start while the preceding kernel drains (never together with a cooperative launch: the
+            // grid is sized from the occupancy query, so it is co-resident once that kernel has left)
+            at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        } else if (c.coop) {
             at[na].id = cudaLaunchAttributeCooperative;
             at[na].val.cooperative = 1;
             ++na;
@@ -1450,6 +1460,7 @@ int cf_decoder_step(int64_t handle, void* stream) {
         p.tp_rank = dc->cfg.tp_rank;
         for (int r = 0; r < dc->cfg.tp_size; ++r) p.tp_peer[r] = dc->tp_peer[r];
         p.tp_epoch_base = dc->tp_count;
+        p.tp_packed = env_int("CFB200_TP_PACKED", 1) != 0;  // must be the same on every rank
     }
     p.layers = dc->layers_d;
     p.tail = dc->tail_d;

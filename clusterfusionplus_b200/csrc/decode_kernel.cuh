@@ -173,7 +173,17 @@ struct Params {
     int tp_size, tp_rank;
     unsigned char* tp_peer[MAX_TP];
     unsigned* tp_epoch_base;    // two local words: [0] running epoch base of the exchanges, [1] launches so far
+    int tp_packed;     // exchange words of one CTA are contiguous (its threads' peer stores coalesce) instead of row-indexed
+    // Launched with programmatic stream serialization: this grid may start while the kernel before it in the
+    // stream is still draining.  Weights are never written on the device, so the producer streams its first
+    // ring-full of P1 stages at once; everything else waits for that kernel (griddepcontrol.wait) first.  The
+    // caller promises that the preceding kernel writes neither seq_len nor the descriptors.
+    int pdl;
+    int merge_seg_max;  // diagnostics: > 0 caps the segments a head's partial records are cut into for the merge (1 = never cut)
 };
+
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Exchange buffer of one rank (H = hidden).  Every word travels with the epoch it belongs
 // to in the same aligned 8-byte store (value, epoch), so a reader that sees the epoch has the
@@ -247,6 +257,7 @@ constexpr int TRACE_EVENTS = 16;
 enum : int {
     TR_START = 0, TR_LN_DONE, TR_P1_DONE, TR_BAR1, TR_P2_DONE, TR_BAR2, TR_X3_BUILT, TR_P3_GEMV, TR_P3_DONE,
     TR_PROD_P1 = 10, TR_PROD_P2, TR_PROD_P3,
+    TR_MERGE_GO = 13, TR_MERGE_POLLED, TR_MERGE_DONE,  // helper warps: P3's attention merge
 };
 __device__ __forceinline__ void trace_mark(const Params& p, int cta, int layer, int ev) {
     if (p.trace) p.trace[(static_cast<size_t>(cta) * (p.n_layers + 1) + layer) * TRACE_EVENTS + ev] = globaltimer_ns();
@@ -368,7 +379,10 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
     return 0.5f * x * (1.0f + tanhf(u));
 }
 
-// 8 rows x 256 K of one slot against this lane's 8 activations
+// 8 rows x 256 K of one slot against this lane's 8 activations.  The two 16-byte activation reads have a
+// 32-byte stride between lanes (two-way bank conflict, 2 of the 34 shared-memory reads of a slot); a layout in
+// two planes ([lane][4] twice per chunk) makes them conflict-free but measured 1.3 % slower per token
+// (2 500 against 2 467 us, alternating processes on one GPU; larger stack frame), so the plain layout stays.
 __device__ __forceinline__ void gemv_slot(const uint8_t* slot, const float* xs, int lane, float (&acc)[GRAN]) {
     const float4 xa = *reinterpret_cast<const float4*>(xs + lane * 8);
     const float4 xb = *reinterpret_cast<const float4*>(xs + lane * 8 + 4);
@@ -752,8 +766,16 @@ struct Producer {
     uint64_t policy;
     AbortCtl ab;
     uint32_t issued;  // stages issued so far
+    int early_left;   // >= 0: stages that may still be issued before waiting for the preceding kernel (Params::pdl)
     __device__ __forceinline__ bool stop() const { return *ab.flag != 0; }
+    __device__ __forceinline__ void depend() {
+        if (early_left >= 0) {
+            griddep_wait();
+            early_left = -1;
+        }
+    }
     __device__ __forceinline__ void acquire() {
+        if (early_left >= 0 && early_left-- == 0) griddep_wait();  // leaves early_left at -1
         mbar_wait(empty_addr + cur.stage * 8, cur.phase ^ 1u, ab, ST_TIMEOUT_EMPTY);
     }
     __device__ __forceinline__ void expect(uint32_t bar, uint32_t bytes) { mbar_arrive_expect_tx(bar, bytes); }
@@ -884,11 +906,10 @@ struct Consumer {
     }
     // Mirror of Producer::rows_phase.  xs = activations in shared memory (KC*256
     // floats); epi(granule index relative to g0=0, row in granule, dot product).
-    // gate_chunk >= 0: before the first use of activation chunk `gate_chunk`, wait (bounded)
-    // on mbarrier gate_bar / gate_parity (the helpers' "chunks from here on are ready").
-    template <class Epi>
-    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi, int gate_chunk = -1,
-                                               uint32_t gate_bar = 0, uint32_t gate_parity = 0) {
+    // gate_chunk >= 0: before the first use of activation chunk `gate_chunk`, all consumer threads call
+    // gate() (wait for the helpers' "chunks from here on are ready", or build those chunks).
+    template <class Epi, class Gate>
+    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi, int gate_chunk, Gate gate) {
         if (cnt <= 0) return;
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = 0;
@@ -899,7 +920,7 @@ struct Consumer {
 #pragma unroll
             for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
             for (int c = 0; c < KC; ++c) {
-                if (c == gate_chunk && r == 0) mbar_wait(gate_bar, gate_parity, ab, ST_TIMEOUT_FULL);
+                if (c == gate_chunk && r == 0) gate();
                 const uint8_t* st = wait_stage();
                 if (!touch_only) {
                     if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
@@ -1020,6 +1041,99 @@ struct Consumer {
 };
 
 // ---------------------------------------------------------------- the kernel
+// P3's attention chunks of xbuf = weighted sums of the partial records (record offsets in offs[], normalised
+// weights in pm[], both complete when this runs).  Run by threads t = 0 .. nthr-1 whose named barrier is bar_id:
+// four consecutive elements per thread, two groups of eight records in flight.  mseg > 1: a vector's records are
+// cut into mseg segments that different threads sum, so that every thread has loads in flight; the segment sums
+// meet in the (idle) auxiliary region of xbuf and are added in segment order.  Not inlined: it runs once per layer
+// and its 16 vectors in flight must not press on the callers' registers.
+struct MergeArgs {
+    float* xbuf;
+    const int* offs;
+    const float* pm;
+    const float* pbase;
+    int aux_off, nve, mseg, pstr, nmid, me, KVW;
+};
+template <int D, int CS>
+__device__ __noinline__ void merge_sums(const MergeArgs& a, int t, int nthr, int bar_id) {
+    constexpr int HPC = (KCHUNK + D - 1) / D + 1;
+    const int nve = a.nve, mseg = a.mseg, pstr = a.pstr;
+    const int seglen = ceil_div(ceil_div(pstr, mseg), 8) * 8;
+    float4* segbuf = reinterpret_cast<float4*>(a.xbuf + a.aux_off);
+    const int nitem = nve * mseg;
+    for (int v0 = t; v0 < nitem; v0 += 2 * nthr) {
+        float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+        int wrow[2], dd[2], dsti[2], jlo[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int item = v0 + u * nthr;
+            const int sg = item / nve, v = item - sg * nve;
+            const int i = v / (KCHUNK / 4), k4 = v - i * (KCHUNK / 4);
+            const int q = a.me + i * CS;
+            const int e = q * KCHUNK + k4 * 4;
+            wrow[u] = -1;
+            dd[u] = 0;
+            jlo[u] = sg * seglen;
+            dsti[u] = (item < nitem) ? (mseg > 1 ? item : (a.nmid + i) * KCHUNK + k4 * 4) : -1;
+            if (item < nitem && e < a.KVW) {
+                const int h = e / D;
+                dd[u] = e - h * D;
+                wrow[u] = (i * HPC + (h - (q * KCHUNK) / D)) * pstr;
+            }
+        }
+        for (int j0 = 0; j0 < seglen; j0 += 8) {
+            float4 vv[2][8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                    vv[u][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const int j = jlo[u] + j0 + jj;
+                    if (wrow[u] >= 0 && j < pstr) {
+                        const int o = a.offs[wrow[u] + j];
+                        if (o >= 0) vv[u][jj] = ld_cg_f32x4(a.pbase + o + dd[u]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+                    const int j = jlo[u] + j0 + jj;
+                    const float w = (wrow[u] >= 0 && j < pstr) ? a.pm[wrow[u] + j] : 0.f;
+                    acc[u].x = fmaf(w, vv[u][jj].x, acc[u].x);
+                    acc[u].y = fmaf(w, vv[u][jj].y, acc[u].y);
+                    acc[u].z = fmaf(w, vv[u][jj].z, acc[u].z);
+                    acc[u].w = fmaf(w, vv[u][jj].w, acc[u].w);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (dsti[u] >= 0) {
+                if (mseg > 1) segbuf[dsti[u]] = acc[u];
+                else *reinterpret_cast<float4*>(a.xbuf + dsti[u]) = acc[u];
+            }
+    }
+    if (mseg > 1) {
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthr) : "memory");
+        for (int v = t; v < nve; v += nthr) {
+            float4 r = segbuf[v];
+            for (int sg = 1; sg < mseg; ++sg) {
+                const float4 o = segbuf[sg * nve + v];
+                r.x += o.x;
+                r.y += o.y;
+                r.z += o.z;
+                r.w += o.w;
+            }
+            const int i = v / (KCHUNK / 4), k4 = v - i * (KCHUNK / 4);
+            *reinterpret_cast<float4*>(a.xbuf + (a.nmid + i) * KCHUNK + k4 * 4) = r;
+        }
+        // the sums are in place for every thread; the auxiliary region may be rewritten
+        asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthr) : "memory");
+    }
+}
+
 template <int D, int CS>
 __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_constant__ Params p) {
     static_assert(D % 8 == 0 && D <= 128, "head_dim must be a multiple of 8, at most 128");
@@ -1050,6 +1164,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     }
     __syncthreads();
     if constexpr (CS > 1) dsm::cluster_sync_all();  // peers' barriers exist before any remote arrive
+    // the launch after this one may take an SM as soon as a CTA of this grid leaves it
+    if (p.pdl && tid == 0) griddep_launch_dependents();
 
     const int seq = p.seq_ptr ? __ldcg(p.seq_ptr) : p.seq_host;
     const int H = p.H, NH = p.NH, R = p.R, F = p.F;
@@ -1175,6 +1291,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         }
     };
 
+    // P3's attention merge (merge_sums above): with many partials per head (few local heads, i.e. tensor parallel)
+    // a vector's records are cut into mseg segments -- and the consumer threads run it, which have nothing else to
+    // do by then (their share of P3's weights is short), instead of the three helper warps.
+    MergeArgs mga;
+    mga.xbuf = sm.xbuf;
+    mga.offs = sm.offs;
+    mga.pm = sm.pm;
+    mga.pbase = (nch == 0) ? p.attn_new : p.attn_part;
+    mga.aux_off = p.aux_off;
+    mga.nve = nattn * (KCHUNK / 4);
+    mga.mseg = (mga.nve > 0) ? max(1, min(ceil_div(pstr, 8), (aux_floats(D) / 4) / mga.nve)) : 1;
+    if (p.merge_seg_max > 0) mga.mseg = min(mga.mseg, p.merge_seg_max);
+    mga.pstr = pstr;
+    mga.nmid = my3 - nattn;
+    mga.me = me;
+    mga.KVW = KVW;
+    const bool merge_by_consumers = mga.mseg > 1;
+    const float* pbase = mga.pbase;
+
     // =========================================================== producer warp
     if (warp == NCWARP) {
         if (lane == 0) {
@@ -1186,6 +1321,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
             pr.policy = l2_policy_evict_first();
             pr.ab = ab;
             pr.issued = 0;
+            // the first ring-full of weight stages does not depend on the kernel before this one
+            pr.early_left = (p.pdl && (p.phase_mask & PH_P1)) ? p.nstage : -1;
+            if (p.pdl && pr.early_left < 0) griddep_wait();
 
             for (int l = 0; l < p.n_layers; ++l) {
                 const LayerDesc* L = p.layers + l;
@@ -1193,6 +1331,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     pr.rows_phase2(&L->tm_qkv, qa, qb - qa, &L->tm_up, ua, ub - ua, KC1);
                     trace_mark(p, cta, l, TR_PROD_P1);
                 }
+                pr.depend();  // key / value tiles and everything after them may come from the preceding kernel
                 if (p.phase_mask & PH_P2) {
                     for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(&L->tm_k, &L->tm_v, t / nch, t % nch);
                     trace_mark(p, cta, l, TR_PROD_P2);
@@ -1240,17 +1379,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         __syncwarp();
     } else if (warp > NCWARP) {
         // ========================================================= helper warps
+        if (p.pdl) griddep_wait();
         // Side work that is pure L2 latency, kept off the consumers' path: in P3, merge the
         // attention partials of all CTAs into this CTA's attention chunks of xbuf.
         const int ht = tid - (NCWARP + 1) * 32;
-        const int nmid = my3 - nattn;
         const int nent = nattn * HPC * pstr;
         // every CTA past P1 <=> the MLP intermediate is complete: one helper thread watches the
         // count and tells the consumers through shared memory, so that they never poll global memory
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
         // Helper warp 0: one thread watches the count, then the warp copies this CTA's MLP chunks into
         // xbuf -- the consumers are in P2 meanwhile (xbuf's chunk area is free once every CTA, this one
-        // included, is past P1) and find their P3 operands in place when they arrive.
+        // included, is past P1) and find their P3 operands in place when they arrive.  In a launch without
+        // P2 the consumers would only wait for that one warp: there it just passes the signal on and the
+        // consumer threads stage the chunks themselves.
+        const bool mid_by_helper = mid_wait && (p.phase_mask & PH_P2);
         auto watch_mid = [&](int l) {
             if (mid_wait && ht < 32) {
                 if (ht == 0) {
@@ -1259,9 +1401,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     __threadfence();
                 }
                 __syncwarp();
-                stage_mid(ht, 32);
-                asm volatile("cp.async.wait_all;" ::: "memory");
-                __syncwarp();
+                if (mid_by_helper) {
+                    stage_mid(ht, 32);
+                    asm volatile("cp.async.wait_all;" ::: "memory");
+                    __syncwarp();
+                }
                 if (ht == 0) mbar_arrive(smem_u32(sm.mid_ready));
             }
         };
@@ -1373,7 +1517,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 sm.offs[it] = off;
             }
             helper_sync(NHTHR);
-            const float* pbase = (nch == 0) ? p.attn_new : p.attn_part;
             constexpr int ML_ITERS = (WTS_SLOTS + NHTHR - 1) / NHTHR;
             uint32_t gpar = 0;
             unsigned nfin = 0;  // partials finished so far (all layers): phase of the hand-over barriers
@@ -1448,6 +1591,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 // the consumers have left P2 of this layer: xbuf's attention chunks are free
                 mbar_wait(smem_u32(sm.h_go), gpar, ab, ST_TIMEOUT_GRID);
                 gpar ^= 1u;
+                if (ht == 0) trace_mark(p, cta, l, TR_MERGE_GO);
                 const unsigned pep = hl_base + static_cast<unsigned>(l) + 1u;
                 // (max, denominator) of every table entry -> normalised weights in pm[]
                 float mreg[ML_ITERS], lreg[ML_ITERS];
@@ -1480,84 +1624,43 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                 }
                 helper_sync(NHTHR);
-                float wn[ML_ITERS];
+                if (ht == 0) trace_mark(p, cta, l, TR_MERGE_POLLED);
+                // normalised weights, one helper warp per (chunk, head) row of the table: lane j holds slots j and
+                // j + 32 (a head has at most MAX_PARTS = 64 partials); maximum and denominator by butterfly
+                // shuffles -- a fixed order, the same in every CTA and on every rank
+                static_assert(MAX_PARTS <= 64, "two slots per lane");
+                {
+                    const int hw = ht >> 5;
+                    const int nrow = nattn * HPC;
+                    for (int r = hw; r < nrow; r += NHWARP) {
+                        const int r0 = r * pstr;
+                        const bool a0 = lane < pstr, a1 = lane + 32 < pstr;
+                        const float m0 = a0 ? sm.pm[r0 + lane] : -INFINITY, m1 = a1 ? sm.pm[r0 + lane + 32] : -INFINITY;
+                        const float l0 = a0 ? sm.pl[r0 + lane] : 0.f, l1 = a1 ? sm.pl[r0 + lane + 32] : 0.f;
+                        float M = fmaxf(m0, m1);
 #pragma unroll
-                for (int k = 0; k < ML_ITERS; ++k) {
-                    const int it = ht + k * NHTHR;
-                    wn[k] = 0.f;
-                    if (it < nent && mreg[k] > -INFINITY) {
-                        const int r0 = (it / pstr) * pstr;
-                        float M = -INFINITY, den = 0.f;
-                        for (int j = 0; j < pstr; ++j) M = fmaxf(M, sm.pm[r0 + j]);
-                        for (int j = 0; j < pstr; ++j) {
-                            const float mj = sm.pm[r0 + j];
-                            if (mj > -INFINITY) den = fmaf(exp2f(mj - M), sm.pl[r0 + j], den);
-                        }
-                        wn[k] = exp2f(mreg[k] - M) / den;
+                        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                        const float e0 = (m0 > -INFINITY) ? exp2f(m0 - M) : 0.f, e1 = (m1 > -INFINITY) ? exp2f(m1 - M) : 0.f;
+                        float den = fmaf(e0, l0, e1 * l1);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+                        __syncwarp();  // every lane has read its m before the slots become weights
+                        if (a0) sm.pm[r0 + lane] = (e0 > 0.f) ? e0 / den : 0.f;
+                        if (a1) sm.pm[r0 + lane + 32] = (e1 > 0.f) ? e1 / den : 0.f;
                     }
-                }
-                helper_sync(NHTHR);  // everyone has read pm before it becomes the weight table
-#pragma unroll
-                for (int k = 0; k < ML_ITERS; ++k) {
-                    const int it = ht + k * NHTHR;
-                    if (it < nent) sm.pm[it] = wn[k];
                 }
                 helper_sync(NHTHR);
-                // weighted sums, four consecutive elements per thread, two groups in flight
-                const int nve = nattn * (KCHUNK / 4);
-                for (int v0 = ht; v0 < nve; v0 += 2 * NHTHR) {
-                    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-                    int wrow[2], dd[2], dsti[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int v = v0 + u * NHTHR;
-                        const int i = v / (KCHUNK / 4), k4 = v - i * (KCHUNK / 4);
-                        const int q = me + i * CS;
-                        const int e = q * KCHUNK + k4 * 4;
-                        wrow[u] = -1;
-                        dd[u] = 0;
-                        dsti[u] = (v < nve) ? (nmid + i) * KCHUNK + k4 * 4 : -1;
-                        if (v < nve && e < KVW) {
-                            const int h = e / D;
-                            dd[u] = e - h * D;
-                            wrow[u] = (i * HPC + (h - (q * KCHUNK) / D)) * pstr;
-                        }
-                    }
-                    for (int j0 = 0; j0 < pstr; j0 += 8) {
-                        float4 vv[2][8];
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) {
-                                vv[u][jj] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (wrow[u] >= 0 && j0 + jj < pstr) {
-                                    const int o = sm.offs[wrow[u] + j0 + jj];
-                                    if (o >= 0) vv[u][jj] = ld_cg_f32x4(pbase + o + dd[u]);
-                                }
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                            for (int jj = 0; jj < 8; ++jj) {
-                                const float w = (wrow[u] >= 0 && j0 + jj < pstr) ? sm.pm[wrow[u] + j0 + jj] : 0.f;
-                                acc[u].x = fmaf(w, vv[u][jj].x, acc[u].x);
-                                acc[u].y = fmaf(w, vv[u][jj].y, acc[u].y);
-                                acc[u].z = fmaf(w, vv[u][jj].z, acc[u].z);
-                                acc[u].w = fmaf(w, vv[u][jj].w, acc[u].w);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < 2; ++u)
-                        if (dsti[u] >= 0) *reinterpret_cast<float4*>(sm.xbuf + dsti[u]) = acc[u];
-                }
+                // the table is complete: either the consumer threads, idle by now, take the sums (many partials
+                // per head), or the helper threads do them while the consumers stream the MLP chunks
+                if (!merge_by_consumers) merge_sums<D, CS>(mga, ht, NHTHR, 2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(sm.attn_ready));
+                if (ht == 0 && !merge_by_consumers) trace_mark(p, cta, l, TR_MERGE_DONE);
             }
         }
     } else {
         // ======================================================= consumer warps
+        if (p.pdl) griddep_wait();
         Consumer co;
         co.ring = sm.ring;
         co.full_addr = smem_u32(sm.full);
@@ -1858,7 +1961,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 // them while the GEMV already runs over the MLP chunks.
                 const int nmid = my3 - nattn;
                 if (tid == 0) mbar_arrive(smem_u32(sm.h_go));
-                if (mid_wait) {
+                if (mid_wait && (p.phase_mask & PH_P2)) {
                     // staged by helper warp 0 while this CTA was still in P2
                 } else if (!(p.p3_flags & F3_MID_F16)) {
                     stage_mid(tid, NCTHR);
@@ -1875,7 +1978,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (i0 + ii < nmid) sm.xbuf[(i0 + ii) * KCHUNK + tid] = v[ii];
                     }
                 }
-                // (3) what the epilogue adds to this thread's output row, fetched early
+                // (3) what the epilogue adds to this thread's output row, fetched before the GEMV.  (Fetching it a
+                // phase earlier, right after the LayerNorm, measured 1.2 % SLOWER per token: the thread stalls
+                // there on the loads, and this point is not on the critical path.)
                 float epi_add = 0.f;
                 {
                     const int nrows_e = (g3b - g3a) * GRAN;
@@ -1901,9 +2006,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (cnt > 0) {
                     if (my3 > 0) {
                         float* rv = sm.recv;
-                        co.rows_phase(cnt, my3, sm.xbuf,
-                                      [&](int g, int r, float v) { dsm::scatter_row<CS>(rv, stride, me, g * GRAN + r, v); },
-                                      nattn > 0 ? nmid : -1, smem_u32(sm.attn_ready), hparity);
+                        co.rows_phase(
+                            cnt, my3, sm.xbuf,
+                            [&](int g, int r, float v) { dsm::scatter_row<CS>(rv, stride, me, g * GRAN + r, v); },
+                            nattn > 0 ? nmid : -1, [&] {
+                                // the helpers' signal: attention chunks merged -- or, with many partials per head,
+                                // only the weight table, and these threads form the sums.  (Probed with a pause:
+                                // eight warps probing an mbarrier back to back take issue slots and shared-memory
+                                // pipe cycles from the helper warps they are waiting for.)
+                                const uint32_t bar = smem_u32(sm.attn_ready);
+                                wait_bounded<POLL_BACKOFF_NS>([&] { return mbar_try_wait(bar, hparity); }, ab, ST_TIMEOUT_FULL);
+                                if (merge_by_consumers) {
+                                    merge_sums<D, CS>(mga, tid, NCTHR, 1);
+                                    if (tid == 0) trace_mark(p, cta, l, TR_MERGE_DONE);
+                                }
+                            });
                     } else {
                         for (int t = tid; t < nrows; t += NCTHR) dsm::scatter_row<CS>(sm.recv, stride, me, t, 0.f);
                     }
@@ -1934,13 +2051,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     const int parity = static_cast<int>(tp_epoch & 1u);
                     if (me + tid * CS < nrows) {
                         const int row = g3a * GRAN + me + tid * CS;
+                        // the word's place in a slot: by row, or (packed) the cluster's row range re-ordered so that
+                        // the words of one CTA are contiguous and its threads' peer stores leave as whole lines
+                        // -- the same permutation on every rank, since the partition is the same
+                        int word = row;
+                        if (p.tp_packed) {
+                            word = g3a * GRAN + tid;
+                            for (int m = 0; m < me; ++m) word += (nrows - m + CS - 1) / CS;
+                        }
                         const float mine = dsm::tree_sum<CS>(sm.recv, stride, tid);
                         for (int r = 0; r < p.tp_size; ++r)
                             if (r != p.tp_rank)
-                                st_ll_sys(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(row) * 8,
+                                st_ll_sys(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(word) * 8,
                                       __float_as_uint(mine), tp_epoch);
                         // all counterparts' words in flight at once; re-read (bounded) until every epoch matches
-                        const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(row) * 8;
+                        const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(word) * 8;
                         uint2 w[MAX_TP];
                         auto fetch = [&]() {
                             bool ok = true;

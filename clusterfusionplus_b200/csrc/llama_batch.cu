@@ -7,6 +7,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -174,7 +175,9 @@ int launch_lb(LbDevice& d, lb::Params& p, cudaStream_t st) {
     at[0].id = cudaLaunchAttributeCooperative;  // the phases meet at grid barriers: all CTAs must be resident
     at[0].val.cooperative = 1;
     lc.attrs = at;
-    lc.numAttrs = 1;
+    // CFB200_COOPERATIVE=0 (profilers): a plain launch; one CTA per SM is resident anyway when nothing else runs
+    static const bool coop = [] { const char* e = getenv("CFB200_COOPERATIVE"); return !(e && e[0] == '0'); }();
+    lc.numAttrs = coop ? 1 : 0;
     void* args[1] = {&p};
     cudaError_t e = cudaLaunchKernelExC(&lc, reinterpret_cast<const void*>(&lb::llama_batch_kernel), args);
     if (e != cudaSuccess)

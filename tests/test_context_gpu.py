@@ -100,6 +100,55 @@ def test_many_contexts_like_a_model(cuda_device):
             destroy(i)
 
 
+def test_programmatic_dependent_launch_chain_is_bitwise_identical(cuda_device, monkeypatch):
+    """CFB200_PDL=1 chains the per-layer launches by programmatic dependent launch (each kernel streams its
+    first weight stages while the one before it drains, and waits for it before touching anything else).
+    Same bits as the plain chain, eagerly and inside a captured CUDA graph."""
+    import clusterfusion as cf
+    create, step, destroy, _, _ = api("2b8")
+    n = 6
+    cases = [make_case("2b8", 40, rows=48, wseed=300 + i) for i in range(n)]
+    for i, (s, w, x, k, v, cos, sin) in enumerate(cases):
+        create(20 + i, k, v, w["qkv_weight"], w["o_weight"], w["mlp_up_weight"], w["mlp_down_weight"], 48)
+    snaps = [(c[3].clone(), c[4].clone()) for c in cases]
+    x0 = cases[0][2].clone()
+
+    def chain():
+        h = x0
+        for i, (s, w, x, k, v, cos, sin) in enumerate(cases):
+            h, _, _ = step(*step_args(20 + i, h, w, k, v, cos, sin, 40))
+        return h.clone()
+
+    def restore():
+        for (s, w, x, k, v, cos, sin), (ks, vs) in zip(cases, snaps):
+            k.copy_(ks), v.copy_(vs)
+
+    try:
+        monkeypatch.setenv("CFB200_PDL", "0")
+        plain = chain()
+        torch.cuda.synchronize()
+        restore()
+        monkeypatch.setenv("CFB200_PDL", "1")
+        for _ in range(3):
+            got = chain()
+            torch.cuda.synchronize()
+            assert torch.equal(got, plain)
+            restore()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = chain()
+        for _ in range(3):
+            restore()
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, plain)
+    finally:
+        monkeypatch.setenv("CFB200_PDL", "0")
+        for i in range(n):
+            destroy(20 + i)
+    assert cf.device_status() == 0
+
+
 def test_real_cuda_graph_replay(cuda_device):
     """Capture graph_decode_step once with device-resident seq_len and RoPE table, then
     replay it for consecutive positions (the reference's mode cannot: it bakes seq_len

@@ -187,3 +187,56 @@ def test_pythia_6b9_shapes_greedy_64_steps_identical(cuda_device):
     assert got == want, f"first mismatch at step {first_diff}; min top-2 gap of the oracle {min(gaps):.4g}, " \
                         f"gap at mismatch {gaps[first_diff]:.4g}"
     assert mx <= MAX_ABS and rl <= 5 * REL_L2, (mx, rl)
+
+
+def test_few_heads_long_context_merge_paths(cuda_device, monkeypatch):
+    """A model with 4 heads (the shape of one rank's shard at 8-way tensor parallelism) and 1 200 cached rows:
+    every head's attention is split into ~10 partial records on as many CTAs, the table of partials per head is
+    long (37 slots), so the records are cut into segments and the CONSUMER threads form the weighted sums.
+    32 greedy tokens identical to the fp32 oracle's; and the same tokens, logits within 1e-3, when the segment
+    count is capped at 1 (CFB200_MERGE_SEG=1: the helper warps sum every record in slot order)."""
+    import clusterfusion as cf
+    dev = cuda_device
+    shape = O.Shape("few-heads", 512, 4, 128, 32, 1024, 1024, layers=3)
+    seed, ctx, steps = 77, 1200, 32
+    layers = [O.make_layer_weights(shape, l, seed=seed, device=dev) for l in range(shape.layers)]
+    head = O.make_head_weights(shape, seed=seed, device=dev)
+    max_seq = ctx + steps + 2
+    om = O.OracleModel(shape, [{n: t.cpu() for n, t in w.items()} for w in layers],
+                       {n: t.cpu() for n, t in head.items()}, max_seq, round_io=False)
+    kv = [O.make_kv_cache(shape, ctx, max_seq, 500 + l, device=dev) for l in range(shape.layers)]
+    for l, (kk, vv) in enumerate(kv):
+        om.load_cache(l, kk, vv, ctx)
+    om.seq_len = ctx
+    want, otok = [], 99
+    logits = None
+    for _ in range(steps):
+        logits, _ = om.step(otok)
+        otok = int(logits.argmax())
+        want.append(otok)
+
+    def rollout(cap):
+        monkeypatch.setenv("CFB200_MERGE_SEG", str(cap))
+        dec, ld, hd, caches = build_decoder(shape, layers, head, max_seq, dev, use_graph=False)
+        for (k, v), (kk, vv) in zip(caches, kv):
+            k.copy_(kk), v.copy_(vv)
+        dec.reset(ctx, 99)
+        got = []
+        for _ in range(steps):
+            dec.step()
+            got.append(int(dec.token.item()))
+        out = dec.logits.float().cpu().clone()
+        dec.close()
+        return got, out
+
+    try:
+        got_seg, log_seg = rollout(0)     # automatic: segments, consumer threads
+        got_one, log_one = rollout(1)     # one segment, helper warps
+    finally:
+        monkeypatch.setenv("CFB200_MERGE_SEG", "0")
+    assert cf.device_status() == 0
+    assert got_seg == want, (got_seg, want)
+    assert got_one == want
+    mx, rl = O.compare(log_seg, logits)
+    assert mx <= MAX_ABS and rl <= 5 * REL_L2, (mx, rl)
+    assert (log_seg - log_one).abs().max().item() <= 1e-3

@@ -84,6 +84,15 @@ def test_drop_in_module_surface():
     assert len(inspect.signature(clusterfusion.pythia_2b8_mlp_only).parameters) == 5
 
 
+def test_transposed_llama_entry_point_is_a_documented_refusal():
+    """The reference's llama_decoder_layer (include/pybind.cpp:66-74) takes transposed weights; the name
+    exists and says which entry point computes the same block."""
+    import clusterfusion
+    assert len(inspect.signature(clusterfusion.llama_decoder_layer).parameters) == 8
+    with pytest.raises(NotImplementedError, match="llama_decoder_layer_sglang"):
+        clusterfusion.llama_decoder_layer(*[None] * 8)
+
+
 def test_cpu_tensors_are_rejected():
     import clusterfusion
     H, F = 2560, 10240
