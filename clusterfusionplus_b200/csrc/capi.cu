@@ -471,6 +471,16 @@ void base_params(Params& p, const CfDims& d, const Workspace& ws) {
     p.amax_idx = ws.amax_idx;
 }
 
+// Tensor map of a key or value cache [kv_rows][heads * head_dim]: boxes of one head x KV_TILE rows.
+int encode_kv(CUtensorMap* tm, const CfDims& d, void* cache, int64_t kv_rows) {
+    const int KVW = d.heads * d.head_dim;
+    // a head's slice of a cache row is head_dim * 2 bytes: promote L2 fetches to 256 B only when
+    // that is a whole number of 256-byte lines (head_dim 128), otherwise fetch exact sectors
+    const CUtensorMapL2promotion kvp =
+        (d.head_dim * 2) % 256 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    return encode_2d(tm, cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE, kvp);
+}
+
 // Build the six tensor maps + pointers of one layer.  Null matrices are skipped.
 int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, void* k_cache, void* v_cache,
                      int64_t kv_rows, int up_rows = 0) {
@@ -481,12 +491,8 @@ int build_layer_desc(LayerDesc& L, const CfDims& d, const CfLayerWeights& w, voi
     if (w.mlp_up_weight && (rc = encode_weight(&L.tm_up, w.mlp_up_weight, d.hidden, up_rows ? up_rows : d.ffn))) return rc;
     if (w.o_weight && (rc = encode_weight(&L.tm_o, w.o_weight, KVW, d.hidden))) return rc;
     if (w.mlp_down_weight && (rc = encode_weight(&L.tm_down, w.mlp_down_weight, d.ffn, d.hidden))) return rc;
-    // a head's slice of a cache row is head_dim * 2 bytes: promote L2 fetches to 256 B only when
-    // that is a whole number of 256-byte lines (head_dim 128), otherwise fetch exact sectors
-    const CUtensorMapL2promotion kvp =
-        (d.head_dim * 2) % 256 == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE;
-    if (k_cache && (rc = encode_2d(&L.tm_k, k_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE, kvp))) return rc;
-    if (v_cache && (rc = encode_2d(&L.tm_v, v_cache, KVW, kv_rows, KVW, d.head_dim, KV_TILE, kvp))) return rc;
+    if (k_cache && (rc = encode_kv(&L.tm_k, d, k_cache, kv_rows))) return rc;
+    if (v_cache && (rc = encode_kv(&L.tm_v, d, v_cache, kv_rows))) return rc;
     L.ln_w = static_cast<const __half*>(w.ln_weight);
     L.ln_b = static_cast<const __half*>(w.ln_bias);
     L.pln_w = static_cast<const __half*>(w.post_ln_weight);
@@ -915,9 +921,15 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
     w.o_weight = weight_o;
     w.ln_weight = rms_input_weight;
     LayerDesc* desc;
-    if ((rc = cached_desc(*ds, d, w, const_cast<void*>(k_cache), const_cast<void*>(v_cache), seq_len, st, &desc))) return rc;
+    // the descriptor holds the weights only (one per layer, whatever the sequence length); the caches, which
+    // this entry point takes with exactly seq_len rows, get their tensor maps in the kernel parameters
+    if ((rc = cached_desc(*ds, d, w, nullptr, nullptr, 0, st, &desc))) return rc;
     Params p;
     base_params(p, d, ds->ws);
+    if ((rc = encode_kv(&p.kv_maps[0], d, const_cast<void*>(k_cache), seq_len))) return rc;
+    if ((rc = encode_kv(&p.kv_maps[1], d, const_cast<void*>(v_cache), seq_len))) return rc;
+    p.kv_inline = 1;
+    p.kv_rows_inline = static_cast<int>(seq_len);
     p.layers = desc;
     p.n_layers = 1;
     p.phase_mask = PH_P1 | PH_P2 | PH_P3;
@@ -1461,6 +1473,7 @@ int cf_decoder_step(int64_t handle, void* stream) {
         for (int r = 0; r < dc->cfg.tp_size; ++r) p.tp_peer[r] = dc->tp_peer[r];
         p.tp_epoch_base = dc->tp_count;
         p.tp_packed = env_int("CFB200_TP_PACKED", 1) != 0;  // must be the same on every rank
+        p.tp_flush = env_int("CFB200_TP_FLUSH", 0) != 0;
     }
     p.layers = dc->layers_d;
     p.tail = dc->tail_d;

@@ -174,12 +174,19 @@ struct Params {
     unsigned char* tp_peer[MAX_TP];
     unsigned* tp_epoch_base;    // two local words: [0] running epoch base of the exchanges, [1] launches so far
     int tp_packed;     // exchange words of one CTA are contiguous (its threads' peer stores coalesce) instead of row-indexed
+    int tp_flush;      // experiment: a system-scope fence after a thread's peer stores (pushes them out at once)
     // Launched with programmatic stream serialization: this grid may start while the kernel before it in the
     // stream is still draining.  Weights are never written on the device, so the producer streams its first
     // ring-full of P1 stages at once; everything else waits for that kernel (griddepcontrol.wait) first.  The
     // caller promises that the preceding kernel writes neither seq_len nor the descriptors.
     int pdl;
     int merge_seg_max;  // diagnostics: > 0 caps the segments a head's partial records are cut into for the merge (1 = never cut)
+    // Single-layer launches whose caches change shape from call to call (the Llama block takes caches of exactly
+    // seq_len rows): the key / value tensor maps travel in the kernel parameters instead of the layer descriptor,
+    // so the descriptor depends on the weights only and nothing is uploaded per call.
+    int kv_inline;       // 1: use kv_maps / kv_rows_inline
+    int kv_rows_inline;  // rows the inline maps cover
+    alignas(64) CUtensorMap kv_maps[2];  // key, value
 };
 
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -906,10 +913,11 @@ struct Consumer {
     }
     // Mirror of Producer::rows_phase.  xs = activations in shared memory (KC*256
     // floats); epi(granule index relative to g0=0, row in granule, dot product).
-    // gate_chunk >= 0: before the first use of activation chunk `gate_chunk`, all consumer threads call
-    // gate() (wait for the helpers' "chunks from here on are ready", or build those chunks).
-    template <class Epi, class Gate>
-    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi, int gate_chunk, Gate gate) {
+    // gate_chunk >= 0: before the first use of activation chunk `gate_chunk`, wait (bounded)
+    // on mbarrier gate_bar / gate_parity (the helpers' "chunks from here on are ready").
+    template <class Epi>
+    __device__ __forceinline__ void rows_phase(int cnt, int KC, const float* xs, Epi epi, int gate_chunk = -1,
+                                               uint32_t gate_bar = 0, uint32_t gate_parity = 0) {
         if (cnt <= 0) return;
         const int nr = ceil_div(cnt, NSLOT), base = cnt / nr, extra = cnt % nr;
         int g = 0;
@@ -920,7 +928,10 @@ struct Consumer {
 #pragma unroll
             for (int i = 0; i < GRAN; ++i) acc0[i] = acc1[i] = 0.f;
             for (int c = 0; c < KC; ++c) {
-                if (c == gate_chunk && r == 0) gate();
+                // (probed with a pause: eight warps probing an mbarrier back to back take issue slots and
+                // shared-memory pipe cycles from the helper warps they are waiting for)
+                if (c == gate_chunk && r == 0)
+                    wait_bounded<POLL_BACKOFF_NS>([&] { return mbar_try_wait(gate_bar, gate_parity); }, ab, ST_TIMEOUT_FULL);
                 const uint8_t* st = wait_stage();
                 if (!touch_only) {
                     if (a0) gemv_slot(st + warp * SLOT_BYTES, xs + c * KCHUNK, lane, acc0);
@@ -1045,8 +1056,10 @@ struct Consumer {
 // weights in pm[], both complete when this runs).  Run by threads t = 0 .. nthr-1 whose named barrier is bar_id:
 // four consecutive elements per thread, two groups of eight records in flight.  mseg > 1: a vector's records are
 // cut into mseg segments that different threads sum, so that every thread has loads in flight; the segment sums
-// meet in the (idle) auxiliary region of xbuf and are added in segment order.  Not inlined: it runs once per layer
-// and its 16 vectors in flight must not press on the callers' registers.
+// meet in the (idle) auxiliary region of xbuf and are added in segment order.  Run by the helper warps.  (Run by
+// the 256 consumer threads instead, which are idle by then on a tensor-parallel shard, it passed its tests but cost
+// more than it saved: as a real function call 7 % per token -- every live register of the streaming loops is saved
+// around the call -- and inlined into the consumers' code it spilled 170 bytes per thread.)
 struct MergeArgs {
     float* xbuf;
     const int* offs;
@@ -1055,7 +1068,7 @@ struct MergeArgs {
     int aux_off, nve, mseg, pstr, nmid, me, KVW;
 };
 template <int D, int CS>
-__device__ __noinline__ void merge_sums(const MergeArgs& a, int t, int nthr, int bar_id) {
+__device__ __forceinline__ void merge_sums(const MergeArgs& a, int t, int nthr, int bar_id) {
     constexpr int HPC = (KCHUNK + D - 1) / D + 1;
     const int nve = a.nve, mseg = a.mseg, pstr = a.pstr;
     const int seglen = ceil_div(ceil_div(pstr, mseg), 8) * 8;
@@ -1174,7 +1187,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         // all CTAs see the same seq, so they all leave together
         int kv_rows_min = 0x7fffffff;
         if (p.phase_mask & PH_P2)
-            for (int l = 0; l < p.n_layers; ++l) kv_rows_min = min(kv_rows_min, p.layers[l].kv_rows);
+            for (int l = 0; l < p.n_layers; ++l) kv_rows_min = min(kv_rows_min, p.kv_inline ? p.kv_rows_inline : p.layers[l].kv_rows);
         const int spare = (p.arch_flags & AF_NO_APPEND) ? 0 : 1;  // a free row for the new token
         if (seq < 0 || ((p.phase_mask & PH_P2) && seq > kv_rows_min - spare)) {
             if (tid == 0) atomicCAS(p.status, 0, ST_BAD_SEQ);
@@ -1291,25 +1304,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         }
     };
 
-    // P3's attention merge (merge_sums above): with many partials per head (few local heads, i.e. tensor parallel)
-    // a vector's records are cut into mseg segments -- and the consumer threads run it, which have nothing else to
-    // do by then (their share of P3's weights is short), instead of the three helper warps.
-    MergeArgs mga;
-    mga.xbuf = sm.xbuf;
-    mga.offs = sm.offs;
-    mga.pm = sm.pm;
-    mga.pbase = (nch == 0) ? p.attn_new : p.attn_part;
-    mga.aux_off = p.aux_off;
-    mga.nve = nattn * (KCHUNK / 4);
-    mga.mseg = (mga.nve > 0) ? max(1, min(ceil_div(pstr, 8), (aux_floats(D) / 4) / mga.nve)) : 1;
-    if (p.merge_seg_max > 0) mga.mseg = min(mga.mseg, p.merge_seg_max);
-    mga.pstr = pstr;
-    mga.nmid = my3 - nattn;
-    mga.me = me;
-    mga.KVW = KVW;
-    const bool merge_by_consumers = mga.mseg > 1;
-    const float* pbase = mga.pbase;
-
     // =========================================================== producer warp
     if (warp == NCWARP) {
         if (lane == 0) {
@@ -1333,7 +1327,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 }
                 pr.depend();  // key / value tiles and everything after them may come from the preceding kernel
                 if (p.phase_mask & PH_P2) {
-                    for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(&L->tm_k, &L->tm_v, t / nch, t % nch);
+                    const CUtensorMap* tmk = p.kv_inline ? &p.kv_maps[0] : &L->tm_k;
+                    const CUtensorMap* tmv = p.kv_inline ? &p.kv_maps[1] : &L->tm_v;
+                    for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(tmk, tmv, t / nch, t % nch);
                     trace_mark(p, cta, l, TR_PROD_P2);
                 }
                 if (p.phase_mask & PH_P3) {
@@ -1384,6 +1380,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
         // attention partials of all CTAs into this CTA's attention chunks of xbuf.
         const int ht = tid - (NCWARP + 1) * 32;
         const int nent = nattn * HPC * pstr;
+        // P3's attention merge (merge_sums above): with many partials per head (few local heads, i.e. tensor parallel)
+        // a vector's records are cut into mseg segments.
+        MergeArgs mga;
+        mga.xbuf = sm.xbuf;
+        mga.offs = sm.offs;
+        mga.pm = sm.pm;
+        mga.pbase = (nch == 0) ? p.attn_new : p.attn_part;
+        mga.aux_off = p.aux_off;
+        mga.nve = nattn * (KCHUNK / 4);
+        mga.mseg = (mga.nve > 0) ? max(1, min(ceil_div(pstr, 8), (aux_floats(D) / 4) / mga.nve)) : 1;
+        if (p.merge_seg_max > 0) mga.mseg = min(mga.mseg, p.merge_seg_max);
+        mga.pstr = pstr;
+        mga.nmid = my3 - nattn;
+        mga.me = me;
+        mga.KVW = KVW;
+        const float* pbase = mga.pbase;
+
         // every CTA past P1 <=> the MLP intermediate is complete: one helper thread watches the
         // count and tells the consumers through shared memory, so that they never poll global memory
         const bool mid_wait = (p.phase_mask & PH_P1) && (p.phase_mask & PH_P3) && !(p.p3_flags & F3_MID_F16);
@@ -1650,12 +1663,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                     }
                 }
                 helper_sync(NHTHR);
-                // the table is complete: either the consumer threads, idle by now, take the sums (many partials
-                // per head), or the helper threads do them while the consumers stream the MLP chunks
-                if (!merge_by_consumers) merge_sums<D, CS>(mga, ht, NHTHR, 2);
+                merge_sums<D, CS>(mga, ht, NHTHR, 2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(sm.attn_ready));
-                if (ht == 0 && !merge_by_consumers) trace_mark(p, cta, l, TR_MERGE_DONE);
+                if (ht == 0) trace_mark(p, cta, l, TR_MERGE_DONE);
             }
         }
     } else {
@@ -2006,21 +2017,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 if (cnt > 0) {
                     if (my3 > 0) {
                         float* rv = sm.recv;
-                        co.rows_phase(
-                            cnt, my3, sm.xbuf,
-                            [&](int g, int r, float v) { dsm::scatter_row<CS>(rv, stride, me, g * GRAN + r, v); },
-                            nattn > 0 ? nmid : -1, [&] {
-                                // the helpers' signal: attention chunks merged -- or, with many partials per head,
-                                // only the weight table, and these threads form the sums.  (Probed with a pause:
-                                // eight warps probing an mbarrier back to back take issue slots and shared-memory
-                                // pipe cycles from the helper warps they are waiting for.)
-                                const uint32_t bar = smem_u32(sm.attn_ready);
-                                wait_bounded<POLL_BACKOFF_NS>([&] { return mbar_try_wait(bar, hparity); }, ab, ST_TIMEOUT_FULL);
-                                if (merge_by_consumers) {
-                                    merge_sums<D, CS>(mga, tid, NCTHR, 1);
-                                    if (tid == 0) trace_mark(p, cta, l, TR_MERGE_DONE);
-                                }
-                            });
+                        co.rows_phase(cnt, my3, sm.xbuf,
+                                      [&](int g, int r, float v) { dsm::scatter_row<CS>(rv, stride, me, g * GRAN + r, v); },
+                                      nattn > 0 ? nmid : -1, smem_u32(sm.attn_ready), hparity);
                     } else {
                         for (int t = tid; t < nrows; t += NCTHR) dsm::scatter_row<CS>(sm.recv, stride, me, t, 0.f);
                     }
@@ -2064,6 +2063,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (r != p.tp_rank)
                                 st_ll_sys(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(word) * 8,
                                       __float_as_uint(mine), tp_epoch);
+                        if (p.tp_flush) __threadfence_system();
                         // all counterparts' words in flight at once; re-read (bounded) until every epoch matches
                         const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(word) * 8;
                         uint2 w[MAX_TP];

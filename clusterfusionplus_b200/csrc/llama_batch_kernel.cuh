@@ -316,7 +316,11 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 // integer instructions per MMA (with descriptors rebuilt from scratch and a division per
                 // step it measured 130 ns per MMA and bound the whole phase): the descriptors' constant
                 // bits are formed once, per MMA only the 16-byte-unit start address is added.
-                const uint32_t idesc = idesc_f16(64, na);
+                // Two weight ranges whose tiles lie back to back in the stage (one K block per stage: [gate rows]
+                // [up rows]) are ONE B operand of 2 * na rows: half the MMAs, and their number is what bounds
+                // this phase (~60 - 80 ns each, whatever N).
+                const bool fuse2 = two && kb == 1 && 2 * na <= 256;
+                const uint32_t idesc = idesc_f16(64, fuse2 ? 2 * na : na);
                 const uint64_t desc_hi = smem_desc_sw128(0);       // everything but the start address
                 const uint32_t setmask = static_cast<uint32_t>(nset - 1);  // nset is 2 or 4
                 const uint32_t a_kb = A_KB_BYTES >> 4, w_kb = static_cast<uint32_t>(na * 128) >> 4;
@@ -337,7 +341,7 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                                 const uint32_t accum = (s0 | j | (k16 & ~static_cast<int>(setmask))) ? 1u : 0u;
                                 const uint64_t adesc = desc_hi | (a_lo + 2u * k16);
                                 umma_f16(d0, adesc, desc_hi | (w_lo + 2u * k16), idesc, accum);
-                                if (two) umma_f16(d0 + na, adesc, desc_hi | (w_lo + w2 + 2u * k16), idesc, accum);
+                                if (two && !fuse2) umma_f16(d0 + na, adesc, desc_hi | (w_lo + w2 + 2u * k16), idesc, accum);
                             }
                             a_lo += a_kb;
                             w_lo += w_kb;

@@ -192,9 +192,9 @@ def test_pythia_6b9_shapes_greedy_64_steps_identical(cuda_device):
 def test_few_heads_long_context_merge_paths(cuda_device, monkeypatch):
     """A model with 4 heads (the shape of one rank's shard at 8-way tensor parallelism) and 1 200 cached rows:
     every head's attention is split into ~10 partial records on as many CTAs, the table of partials per head is
-    long (37 slots), so the records are cut into segments and the CONSUMER threads form the weighted sums.
+    long (39 slots), so the merge cuts each vector's records into segments summed by different helper threads.
     32 greedy tokens identical to the fp32 oracle's; and the same tokens, logits within 1e-3, when the segment
-    count is capped at 1 (CFB200_MERGE_SEG=1: the helper warps sum every record in slot order)."""
+    count is capped at 1 (CFB200_MERGE_SEG=1: every record of a vector summed by one thread in slot order)."""
     import clusterfusion as cf
     dev = cuda_device
     shape = O.Shape("few-heads", 512, 4, 128, 32, 1024, 1024, layers=3)
@@ -230,8 +230,8 @@ def test_few_heads_long_context_merge_paths(cuda_device, monkeypatch):
         return got, out
 
     try:
-        got_seg, log_seg = rollout(0)     # automatic: segments, consumer threads
-        got_one, log_one = rollout(1)     # one segment, helper warps
+        got_seg, log_seg = rollout(0)     # automatic: five segments per vector
+        got_one, log_one = rollout(1)     # one segment
     finally:
         monkeypatch.setenv("CFB200_MERGE_SEG", "0")
     assert cf.device_status() == 0

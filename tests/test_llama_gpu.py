@@ -50,6 +50,35 @@ def test_llama_attention_block_vs_oracle(cuda_device, seq):
     assert torch.equal(t["k"], k0) and torch.equal(t["v"], v0)   # caches are read-only for this op
 
 
+def test_llama_block_over_growing_caches_needs_no_upload(cuda_device):
+    """A decode loop hands this entry point caches of exactly seq_len rows, one row longer every token
+    (include/5090/llama/llama_kernel_dispatch.cu:35 takes SEQ_LEN from k_cache.size(0)).  The key / value
+    tensor maps travel in the kernel parameters, so after the first call with a set of weights nothing is
+    uploaded any more: every later length can be CAPTURED into a CUDA graph (an upload would be refused there)
+    and the replay matches the eager call and the oracle."""
+    import clusterfusion as cf
+    t = make(300, cuda_device, seed=9)
+    cf.llama_decoder_layer_sglang(t["x"], t["res"].clone(), t["wqkv"], t["wo"], t["k"][:200], t["v"][:200], t["g"], 1e-6,
+                                  t["cos"], t["sin"])             # first call with these weights: descriptor upload
+    torch.cuda.synchronize()
+    for seq in (201, 202, 257, 300):
+        k, v = t["k"][:seq], t["v"][:seq]
+        eager = cf.llama_decoder_layer_sglang(t["x"], t["res"].clone(), t["wqkv"], t["wo"], k, v, t["g"], 1e-6, t["cos"], t["sin"])
+        eager = [e.clone() for e in eager]
+        res = t["res"].clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = cf.llama_decoder_layer_sglang(t["x"], res, t["wqkv"], t["wo"], k, v, t["g"], 1e-6, t["cos"], t["sin"])
+        res.copy_(t["res"])
+        g.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(out, eager):
+            assert torch.equal(a, b)
+        ro, _, _, _ = L.llama_attn_block_fp32(t["x"], t["res"], t["wqkv"], t["wo"], k, v, t["g"], 1e-6, t["cos"], t["sin"])
+        assert O.compare(out[0], ro)[1] <= REL_L2
+    assert cf.device_status() == 0
+
+
 def test_llama_deterministic_and_checked(cuda_device):
     import clusterfusion as cf
     t = make(777, cuda_device, seed=1)
