@@ -1472,8 +1472,8 @@ int cf_decoder_step(int64_t handle, void* stream) {
         p.tp_rank = dc->cfg.tp_rank;
         for (int r = 0; r < dc->cfg.tp_size; ++r) p.tp_peer[r] = dc->tp_peer[r];
         p.tp_epoch_base = dc->tp_count;
-        p.tp_packed = env_int("CFB200_TP_PACKED", 1) != 0;  // must be the same on every rank
-        p.tp_flush = env_int("CFB200_TP_FLUSH", 0) != 0;
+        // experiment switch (must be equal on every rank): no difference measured at 2 GPUs, so off
+        p.tp_packed = env_int("CFB200_TP_PACKED", 0) != 0;
     }
     p.layers = dc->layers_d;
     p.tail = dc->tail_d;

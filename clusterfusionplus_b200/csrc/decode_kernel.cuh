@@ -174,7 +174,6 @@ struct Params {
     unsigned char* tp_peer[MAX_TP];
     unsigned* tp_epoch_base;    // two local words: [0] running epoch base of the exchanges, [1] launches so far
     int tp_packed;     // exchange words of one CTA are contiguous (its threads' peer stores coalesce) instead of row-indexed
-    int tp_flush;      // experiment: a system-scope fence after a thread's peer stores (pushes them out at once)
     // Launched with programmatic stream serialization: this grid may start while the kernel before it in the
     // stream is still draining.  Weights are never written on the device, so the producer streams its first
     // ring-full of P1 stages at once; everything else waits for that kernel (griddepcontrol.wait) first.  The
@@ -2063,7 +2062,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                             if (r != p.tp_rank)
                                 st_ll_sys(p.tp_peer[r] + tl.partial_off(parity, p.tp_rank) + static_cast<size_t>(word) * 8,
                                       __float_as_uint(mine), tp_epoch);
-                        if (p.tp_flush) __threadfence_system();
+                        // (no fence after them: a system-scope fence here measured 1.5 us SLOWER per exchange)
                         // all counterparts' words in flight at once; re-read (bounded) until every epoch matches
                         const unsigned char* mybuf = p.tp_peer[p.tp_rank] + static_cast<size_t>(word) * 8;
                         uint2 w[MAX_TP];

@@ -47,7 +47,7 @@ int encode_sw128(CUtensorMap* tm, const void* ptr, int rank, const cuuint64_t* d
     CfEncodeTiledFn enc = cf_host_encode_fn();
     if (!enc) return cf_host_fail(CF_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return cf_host_fail(CF_ERR_INVALID, "tensor base not 16-byte aligned");
-    cuuint32_t es[3] = {1, 1, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(ptr), dims, strides,
                      box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -106,6 +106,7 @@ int lb_device(cudaStream_t st, LbDevice** out) {
 // Tensor maps and stage geometry of one weight matrix [rows, cols] whose rows are split over `grid` CTAs in 8-row
 // granules, `ranges` row ranges per CTA (2: the gate / up halves of a merged matrix, rows = rows of one half).
 int weight_maps(LbDevice& d, const void* w, int64_t rows, int64_t cols, int ranges, lb::WMaps* out) {
+    if (ranges != 1 && ranges != 2) return cf_host_fail(CF_ERR_INVALID, "%d row ranges per CTA", ranges);
     auto key = std::make_tuple(w, rows, cols, ranges);
     auto it = d.wmaps.find(key);
     if (it == d.wmaps.end()) {
@@ -122,16 +123,38 @@ int weight_maps(LbDevice& d, const void* w, int64_t rows, int64_t cols, int rang
         if (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES)
             return cf_host_fail(CF_ERR_UNSUPPORTED, "a ring stage cannot hold %d weight rows", nr_max);
         m.kb = kb;
-        m.nset = nr_max <= 128 ? 4 : 2;
-        // {64 K elements, rows, K / 64 blocks}: strides of dimension 1 (a row) and 2 (the next 64 columns)
-        const int64_t all_rows = ranges * rows;
-        cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(all_rows), static_cast<cuuint64_t>(nkb)};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+        // Accumulator sets: consecutive MMAs go to different sets of tensor-memory columns, so that each is an
+        // independent chain (an MMA of this size is latency-, not throughput-bound).  As many as fit: a set is
+        // 512 / nset columns wide and must hold the CTA's rows; every set must be written in every stage
+        // (4 MMAs per K block); a power of two.  CFB200_LB_NSET caps it (experiments).
+        {
+            int cap = 512 / nr_max;
+            if (cap > 4 * kb) cap = 4 * kb;
+            if (cap > 16) cap = 16;
+            const char* e = getenv("CFB200_LB_NSET");
+            if (e && atoi(e) > 0 && atoi(e) < cap) cap = atoi(e);
+            m.nset = 1;
+            while (2 * m.nset <= cap) m.nset *= 2;
+        }
+        // {64 K elements, rows, K / 64 blocks}: strides of dimension 1 (a row) and 2 (the next 64 columns).  With
+        // two ranges (the gate and up halves of a merged matrix) the half is a dimension of its own between
+        // them, {64, rows, 2, K / 64}: ONE copy then brings, K block by K block, the CTA's gate rows followed
+        // by its up rows -- a single B operand of 2 r rows for the tensor core.
         for (int v = 0; v < 2; ++v) {
             const int r = m.rows_lo + 8 * v;
             if (r == 0) continue;  // never used: every CTA then holds rows_lo + 8 rows or none
-            cuuint32_t box[3] = {64, static_cast<cuuint32_t>(r), static_cast<cuuint32_t>(kb)};
-            int rc = encode_sw128(v ? &m.hi : &m.lo, w, 3, dims, strides, box);
+            int rc;
+            if (ranges == 2) {
+                cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(rows), 2, static_cast<cuuint64_t>(nkb)};
+                cuuint64_t strides[3] = {static_cast<cuuint64_t>(cols) * 2, static_cast<cuuint64_t>(rows) * cols * 2, 128};
+                cuuint32_t box[4] = {64, static_cast<cuuint32_t>(r), 2, static_cast<cuuint32_t>(kb)};
+                rc = encode_sw128(v ? &m.hi : &m.lo, w, 4, dims, strides, box);
+            } else {
+                cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(nkb)};
+                cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+                cuuint32_t box[3] = {64, static_cast<cuuint32_t>(r), static_cast<cuuint32_t>(kb)};
+                rc = encode_sw128(v ? &m.hi : &m.lo, w, 3, dims, strides, box);
+            }
             if (rc) return rc;
         }
         it = d.wmaps.emplace(key, m).first;

@@ -44,8 +44,8 @@ constexpr int NCW = 8;                // consumer warps (attention arithmetic, n
 constexpr int NCT = NCW * 32;
 constexpr int NGW = 4;                // warps that gather K/V rows in the attention phase: the TMA warp, the MMA warp, two more
 constexpr int THREADS = NCT + NGW * 32;
-constexpr int NSTAGE = 5;
-constexpr int STAGE_BYTES = 40 * 1024;
+constexpr int NSTAGE = 4;
+constexpr int STAGE_BYTES = 44 * 1024;  // two K blocks of the widest tile (16 + 2 x 80 rows) fit: half the copies per byte
 constexpr int A_KB_BYTES = 16 * 128;  // one 64-wide K block of the activation tile: 16 rows x 128 bytes
 constexpr int KV_ROWS = 128;          // cache rows per attention item
 constexpr int REC = D + 4;            // partial record: D numerators, max, denominator, pad
@@ -154,6 +154,13 @@ __device__ __forceinline__ void tma3d(uint32_t dst, const void* tmap, int x, int
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma4d(uint32_t dst, const void* tmap, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
         : "memory");
 }
 
@@ -307,8 +314,8 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     const uint32_t sb = pr.base + pr.stage * STAGE_BYTES;
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kb) * (A_KB_BYTES + NR * 128));
                     tma2d(sb, am, 0, st * kb * 16, bar);
-                    tma3d(sb + kb * A_KB_BYTES, tw, 0, ra0, st * kb, bar);
-                    if (two) tma3d(sb + kb * (A_KB_BYTES + na * 128), tw, 0, rb0, st * kb, bar);
+                    if (two) tma4d(sb + kb * A_KB_BYTES, tw, 0, ra0, 0, st * kb, bar);  // [K block][gate rows | up rows]
+                    else tma3d(sb + kb * A_KB_BYTES, tw, 0, ra0, st * kb, bar);
                     pr.advance();
                 }
             } else if (warp == NCW + 1 && lane == 0) {
@@ -316,15 +323,12 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 // integer instructions per MMA (with descriptors rebuilt from scratch and a division per
                 // step it measured 130 ns per MMA and bound the whole phase): the descriptors' constant
                 // bits are formed once, per MMA only the 16-byte-unit start address is added.
-                // Two weight ranges whose tiles lie back to back in the stage (one K block per stage: [gate rows]
-                // [up rows]) are ONE B operand of 2 * na rows: half the MMAs, and their number is what bounds
-                // this phase (~60 - 80 ns each, whatever N).
-                const bool fuse2 = two && kb == 1 && 2 * na <= 256;
-                const uint32_t idesc = idesc_f16(64, fuse2 ? 2 * na : na);
+                // Two weight ranges arrive K block by K block as [gate rows][up rows]: ONE B operand of 2 * na rows
+                // (the host refuses more than 256 rows per CTA).
+                const uint32_t idesc = idesc_f16(64, NR);
                 const uint64_t desc_hi = smem_desc_sw128(0);       // everything but the start address
-                const uint32_t setmask = static_cast<uint32_t>(nset - 1);  // nset is 2 or 4
-                const uint32_t a_kb = A_KB_BYTES >> 4, w_kb = static_cast<uint32_t>(na * 128) >> 4;
-                const uint32_t w2 = static_cast<uint32_t>(kb * na * 128) >> 4;  // second weight range
+                const uint32_t setmask = static_cast<uint32_t>(nset - 1);  // nset is a power of two, at most 4 * kb
+                const uint32_t a_kb = A_KB_BYTES >> 4, w_kb = static_cast<uint32_t>(NR * 128) >> 4;
                 for (int s0 = 0; s0 < nst; ++s0) {
                     mbar_wait(cr.full + cr.stage * 8, cr.phase, ab, ST_TIMEOUT_FULL);
                     if (*ab.flag) break;
@@ -336,12 +340,12 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                         if (j < kb) {
 #pragma unroll
                             for (int k16 = 0; k16 < 4; ++k16) {
-                                const uint32_t d0 = tmem_base + (static_cast<uint32_t>(k16) & setmask) * set_stride;
+                                const uint32_t idx = static_cast<uint32_t>(j * 4 + k16);  // MMA of this stage
+                                const uint32_t d0 = tmem_base + (idx & setmask) * set_stride;
                                 // the first MMA into each set overwrites, all later ones accumulate
-                                const uint32_t accum = (s0 | j | (k16 & ~static_cast<int>(setmask))) ? 1u : 0u;
+                                const uint32_t accum = (s0 != 0 || (idx & ~setmask) != 0) ? 1u : 0u;
                                 const uint64_t adesc = desc_hi | (a_lo + 2u * k16);
                                 umma_f16(d0, adesc, desc_hi | (w_lo + 2u * k16), idesc, accum);
-                                if (two && !fuse2) umma_f16(d0 + na, adesc, desc_hi | (w_lo + w2 + 2u * k16), idesc, accum);
                             }
                             a_lo += a_kb;
                             w_lo += w_kb;
@@ -360,15 +364,22 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     for (int c0 = 0; c0 < na; c0 += 8) {
                         float v[8], u[8];
                         tmem_ld8(tmem_base + c0, v);
-                        tmem_ld8(tmem_base + (two ? na + c0 : c0), u);
-                        for (int q = 1; q < nset; ++q) {
-                            float v2[8], u2[8];
-                            tmem_ld8(tmem_base + q * set_stride + c0, v2);
-                            tmem_ld8(tmem_base + q * set_stride + (two ? na + c0 : c0), u2);
+                        if (two) {
+                            tmem_ld8(tmem_base + na + c0, u);
+                        } else {
 #pragma unroll
-                            for (int k = 0; k < 8; ++k) {
-                                v[k] += v2[k];
-                                u[k] += u2[k];
+                            for (int k = 0; k < 8; ++k) u[k] = 0.f;
+                        }
+                        for (int q = 1; q < nset; ++q) {
+                            float v2[8];
+                            tmem_ld8(tmem_base + q * set_stride + c0, v2);
+#pragma unroll
+                            for (int k = 0; k < 8; ++k) v[k] += v2[k];
+                            if (two) {
+                                float u2[8];
+                                tmem_ld8(tmem_base + q * set_stride + na + c0, u2);
+#pragma unroll
+                                for (int k = 0; k < 8; ++k) u[k] += u2[k];
                             }
                         }
                         epi(c0, v, u);
