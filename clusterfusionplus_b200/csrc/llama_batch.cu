@@ -26,7 +26,7 @@ struct LbDevice {
     int sm_count = 0;
     char* base = nullptr;
     __half *y16 = nullptr, *attn16 = nullptr, *mid16 = nullptr;
-    float *qkv32 = nullptr, *records = nullptr;
+    float *qkv32 = nullptr, *records = nullptr, *split32 = nullptr;
     unsigned* sync = nullptr;
     int* status = nullptr;
     std::map<std::tuple<const void*, int64_t, int64_t, int>, lb::WMaps> wmaps;   // (weights, rows, cols, ranges per CTA)
@@ -38,6 +38,7 @@ constexpr int LB_MAX_DEVICES = 64;
 constexpr int LB_H = 4096, LB_NH = 32;      // include/5090/llama/config.h:1-4 of the reference
 constexpr int LB_MAX_F = 16384;
 constexpr int LB_MAX_GRID = 256;
+constexpr int LB_MAX_KSPLIT = 4;   // K slices of a narrow projection (groups of CTAs share a row range)
 LbDevice g_lb[LB_MAX_DEVICES];
 std::mutex g_lb_mu;
 
@@ -81,7 +82,8 @@ int lb_device(cudaStream_t st, LbDevice** out) {
         const size_t o_y = 0, o_attn = o_y + up256(sizeof(__half) * 16 * LB_H), o_mid = o_attn + up256(sizeof(__half) * 16 * LB_H);
         const size_t o_qkv = o_mid + up256(sizeof(__half) * 16 * LB_MAX_F);
         const size_t o_rec = o_qkv + up256(sizeof(float) * 16 * 3 * LB_H);
-        const size_t o_sync = o_rec + up256(sizeof(float) * (16 * LB_NH + LB_MAX_GRID) * lb::REC);
+        const size_t o_split = o_rec + up256(sizeof(float) * (16 * LB_NH + LB_MAX_GRID) * lb::REC);
+        const size_t o_sync = o_split + up256(sizeof(float) * LB_MAX_KSPLIT * 16 * LB_H);
         const size_t total = o_sync + 256;
         LB_CUDA(cudaMalloc(&d.base, total));
         LB_CUDA(cudaMemset(d.base, 0, total));
@@ -90,6 +92,7 @@ int lb_device(cudaStream_t st, LbDevice** out) {
         d.mid16 = reinterpret_cast<__half*>(d.base + o_mid);
         d.qkv32 = reinterpret_cast<float*>(d.base + o_qkv);
         d.records = reinterpret_cast<float*>(d.base + o_rec);
+        d.split32 = reinterpret_cast<float*>(d.base + o_split);
         d.sync = reinterpret_cast<unsigned*>(d.base + o_sync);
         d.status = reinterpret_cast<int*>(d.base + o_sync + 16);
         LB_CUDA(cudaFuncSetAttribute(lb::llama_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -107,19 +110,33 @@ int lb_device(cudaStream_t st, LbDevice** out) {
 // granules, `ranges` row ranges per CTA (2: the gate / up halves of a merged matrix, rows = rows of one half).
 int weight_maps(LbDevice& d, const void* w, int64_t rows, int64_t cols, int ranges, lb::WMaps* out) {
     if (ranges != 1 && ranges != 2) return cf_host_fail(CF_ERR_INVALID, "%d row ranges per CTA", ranges);
-    auto key = std::make_tuple(w, rows, cols, ranges);
+    // Narrow matrices -- fewer than 40 rows per CTA -- are cut along K as well: groups of ksplit CTAs share a row
+    // range ksplit times as long (K / 16 MMAs per CTA whatever their width is what bounds such a projection).
+    // Only for matrices with H output rows (the scratch and the kernel's regrouping assume it).
+    int ksplit = 1;
+    {
+        const char* e = getenv("CFB200_LB_KSPLIT");
+        const int want = e ? atoi(e) : LB_MAX_KSPLIT;
+        if (ranges == 1 && rows == LB_H && rows / d.sm_count < 40 && want > 1 && want <= LB_MAX_KSPLIT &&
+            d.sm_count % want == 0 && (cols / 64) >= 4 * want)
+            ksplit = want;
+    }
+    const int ngroups = d.sm_count / ksplit;
+    auto key = std::make_tuple(w, rows, cols, ranges * 16 + ksplit);
     auto it = d.wmaps.find(key);
     if (it == d.wmaps.end()) {
         if (d.wmaps.size() >= 4096) d.wmaps.clear();  // maps are host objects: nothing in flight refers to them
         lb::WMaps m;
         memset(&m, 0, sizeof(m));
         const int64_t ng = rows / 8;
-        m.rows_lo = static_cast<int>(ng / d.sm_count) * 8;
+        m.rows_lo = static_cast<int>(ng / ngroups) * 8;
+        m.ksplit = ksplit;
         const int nr_max = ranges * (m.rows_lo + 8);
         if (nr_max > 256) return cf_host_fail(CF_ERR_UNSUPPORTED, "%d weight rows per CTA (at most 256)", nr_max);
         const int nkb = static_cast<int>(cols / 64);
         int kb = 4;
-        while (kb > 1 && (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES || (nkb % kb) != 0)) kb >>= 1;
+        // (an unsplit K must be a whole number of stages; a slice's last stage may be ragged)
+        while (kb > 1 && (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES || (ksplit == 1 && (nkb % kb) != 0))) kb >>= 1;
         if (kb * (lb::A_KB_BYTES + nr_max * 128) > lb::STAGE_BYTES)
             return cf_host_fail(CF_ERR_UNSUPPORTED, "a ring stage cannot hold %d weight rows", nr_max);
         m.kb = kb;
@@ -185,6 +202,7 @@ int launch_lb(LbDevice& d, lb::Params& p, cudaStream_t st) {
     p.attn16 = d.attn16;
     p.mid16 = d.mid16;
     p.qkv32 = d.qkv32;
+    p.split32 = d.split32;
     p.records = d.records;
     p.sync = d.sync;
     p.status = d.status;

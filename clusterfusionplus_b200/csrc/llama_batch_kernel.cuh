@@ -62,7 +62,7 @@ struct WMaps {
     int rows_lo;  // box rows of `lo`; `hi` has rows_lo + 8
     int kb;       // K blocks per ring stage (box depth of the maps, and of the matching activation map)
     int nset;     // accumulator sets the K steps alternate between (independent MMA chains), summed in the epilogue
-    int pad_;
+    int ksplit;   // > 1: K is cut into ksplit slices over CTAs that share a row group (narrow matrices); partials meet in global memory
 };
 
 struct alignas(64) Params {
@@ -83,6 +83,7 @@ struct alignas(64) Params {
     // scratch
     __half *y16, *attn16, *mid16;  // K-block-major activations of H, H and F columns (see a_idx)
     float* qkv32;                  // [16, 3H]
+    float* split32;                // [ksplit][16][H] fp32 partial outputs of a K-split projection
     float* records;                // [B * NH + grid][REC]
     unsigned* sync;                // [0] barrier count, [1] exit count
     int* status;
@@ -294,11 +295,26 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
     // of rows from rb0: gate / up pairs) against the activations of all sequences over K columns.  All lanes
     // of warp 0 call epi(col0, v, u) for every group of 8 accumulator columns of the first range: v = the 8
     // values of this lane's sequence, u = the same columns of the second range (v again without one).
-    auto gemm_phase = [&](const WMaps* wm, const CUtensorMap* am, int K, int ra0, int ra1, int rb0, bool two, auto epi) {
+    auto gemm_phase = [&](const WMaps* wm, const CUtensorMap* am, int K, int ra0_in, int ra1_in, int rb0, bool two, auto epi) {
+        // Narrow matrices (a few dozen rows per CTA) are bound by the NUMBER of MMAs, K / 16 per CTA whatever their
+        // width: there the CTAs are grouped by ksplit, a group shares a row range ksplit times as long and each
+        // member takes one slice of K; the partial outputs meet in global memory and, after a grid barrier, every
+        // CTA adds the slices of its own (unsplit) rows in slice order and applies the epilogue.
+        const int S = wm->ksplit > 1 ? wm->ksplit : 1;
+        int ra0 = ra0_in, ra1 = ra1_in, blk0 = 0, nblk = K / 64, kslice = 0;
+        if (S > 1) {
+            const int rg = cta / S, NGR = G / S, NGt = p.H / 8;  // K-split projections all have H output rows
+            kslice = cta - rg * S;
+            ra0 = pbegin(rg, NGt, NGR) * 8;
+            ra1 = pbegin(rg + 1, NGt, NGR) * 8;
+            blk0 = pbegin(kslice, K / 64, S);
+            nblk = pbegin(kslice + 1, K / 64, S) - blk0;
+            if (rg >= NGR) ra1 = ra0;  // CTAs beyond the last whole group (none when ksplit divides the grid)
+        }
         const int na = ra1 - ra0, NR = two ? 2 * na : na;
         const CUtensorMap* tw = (na == wm->rows_lo) ? &wm->lo : &wm->hi;
         const int kb = wm->kb, nset = wm->nset, set_stride = TMEM_COLS / nset;
-        const int nst = (K / 64) / kb;
+        const int nst = (nblk + kb - 1) / kb;  // the last stage of a slice may hold fewer than kb of ITS blocks
         // Every CTA needs the same activation tiles; walking K in the same order they would all ask L2 for the
         // same lines at the same moment.  CTA c starts at stage c * nst / G of the K loop and wraps around, so
         // the CTAs are spread over the whole activation matrix (the sum order of a row is fixed by its CTA).
@@ -313,9 +329,9 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     const uint32_t bar = pr.full + pr.stage * 8;
                     const uint32_t sb = pr.base + pr.stage * STAGE_BYTES;
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(kb) * (A_KB_BYTES + NR * 128));
-                    tma2d(sb, am, 0, st * kb * 16, bar);
-                    if (two) tma4d(sb + kb * A_KB_BYTES, tw, 0, ra0, 0, st * kb, bar);  // [K block][gate rows | up rows]
-                    else tma3d(sb + kb * A_KB_BYTES, tw, 0, ra0, st * kb, bar);
+                    tma2d(sb, am, 0, (blk0 + st * kb) * 16, bar);
+                    if (two) tma4d(sb + kb * A_KB_BYTES, tw, 0, ra0, 0, blk0 + st * kb, bar);  // [K block][gate rows | up rows]
+                    else tma3d(sb + kb * A_KB_BYTES, tw, 0, ra0, blk0 + st * kb, bar);
                     pr.advance();
                 }
             } else if (warp == NCW + 1 && lane == 0) {
@@ -329,7 +345,10 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                 const uint64_t desc_hi = smem_desc_sw128(0);       // everything but the start address
                 const uint32_t setmask = static_cast<uint32_t>(nset - 1);  // nset is a power of two, at most 4 * kb
                 const uint32_t a_kb = A_KB_BYTES >> 4, w_kb = static_cast<uint32_t>(NR * 128) >> 4;
+                uint32_t nmma = 0;  // MMAs issued so far in this phase
                 for (int s0 = 0; s0 < nst; ++s0) {
+                    const int st = (s0 + rot) % nst;
+                    const int jn = min(kb, nblk - st * kb);  // blocks of this stage that belong to this CTA's slice
                     mbar_wait(cr.full + cr.stage * 8, cr.phase, ab, ST_TIMEOUT_FULL);
                     if (*ab.flag) break;
                     tc_fence_after();
@@ -337,13 +356,13 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                     uint32_t a_lo = sb >> 4, w_lo = (sb + kb * A_KB_BYTES) >> 4;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (j < kb) {
+                        if (j < jn) {
 #pragma unroll
                             for (int k16 = 0; k16 < 4; ++k16) {
-                                const uint32_t idx = static_cast<uint32_t>(j * 4 + k16);  // MMA of this stage
-                                const uint32_t d0 = tmem_base + (idx & setmask) * set_stride;
+                                const uint32_t d0 = tmem_base + (nmma & setmask) * set_stride;
                                 // the first MMA into each set overwrites, all later ones accumulate
-                                const uint32_t accum = (s0 != 0 || (idx & ~setmask) != 0) ? 1u : 0u;
+                                const uint32_t accum = (nmma > setmask) ? 1u : 0u;
+                                ++nmma;
                                 const uint64_t adesc = desc_hi | (a_lo + 2u * k16);
                                 umma_f16(d0, adesc, desc_hi | (w_lo + 2u * k16), idesc, accum);
                             }
@@ -382,12 +401,41 @@ __global__ void __launch_bounds__(THREADS, 1) llama_batch_kernel(const __grid_co
                                 for (int k = 0; k < 8; ++k) u[k] += u2[k];
                             }
                         }
-                        epi(c0, v, u);
+                        if (S > 1) {
+                            // this slice's share of the rows' dot products: added to the other slices' below
+                            if (lane < B) {
+                                float* dst = p.split32 + (static_cast<size_t>(kslice) * MAXB + lane) * p.H + ra0 + c0;
+                                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                                *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                            }
+                        } else {
+                            epi(c0, v, u);
+                        }
                     }
                 }
                 tc_fence_before();
             }
             acc_phase ^= 1u;
+        }
+        if (S > 1) {
+            grid_barrier();
+            // every CTA: its own rows of the unsplit partition, slices added in slice order
+            if (warp == 0 && !*ab.flag) {
+                for (int c0 = 0; c0 < ra1_in - ra0_in; c0 += 8) {
+                    float v[8], u[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[k] = u[k] = 0.f;
+                    if (lane < B) {
+                        for (int q = 0; q < S; ++q) {
+                            const float* src = p.split32 + (static_cast<size_t>(q) * MAXB + lane) * p.H + ra0_in + c0;
+                            const float4 a = ld_cg_f32x4(src), b = ld_cg_f32x4(src + 4);
+                            v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+                            v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+                        }
+                    }
+                    epi(c0, v, u);
+                }
+            }
         }
     };
 
