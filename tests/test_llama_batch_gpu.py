@@ -110,6 +110,34 @@ def test_mlp_block_batch_vs_oracle(cuda_device, weights, batch):
     assert torch.equal(res_out.cpu().float(), rs)
 
 
+@pytest.mark.parametrize("ksplit", [1, 2])
+def test_narrow_projections_without_and_with_two_k_slices(cuda_device, weights, ksplit, monkeypatch):
+    """The down and output projections (28 rows per CTA) are cut along K over groups of CTAs by default (four
+    slices, a reduction pass); CFB200_LB_KSPLIT selects the unsplit form (1) or two slices.  Same oracle bar."""
+    import clusterfusion as cf
+    dev = cuda_device
+    monkeypatch.setenv("CFB200_LB_KSPLIT", str(ksplit))
+    wd = weights["wd"].clone()          # new tensors: the tensor maps (and their slice count) are cached per tensor
+    wo = weights["wo"].clone()
+    x = O.seeded_normal((5, H), 81, device=dev)
+    res = O.seeded_normal((5, H), 82, device=dev)
+    out, res_out = cf.llama_mlp_batch_sglang(x, res, weights["wgu"], wd, weights["g2"], EPS)
+    ro, rs = LO.llama_mlp_block_batch_fp32(x, res, weights["wgu"], wd, weights["g2"], EPS)
+    close(out, ro, "mlp output")
+    c = make_pool_case([300, 17, 2048], 77, dev)
+    kptrs = torch.tensor([p[0].data_ptr() for p in c["pools"]], dtype=torch.int64, device=dev)
+    vptrs = torch.tensor([p[1].data_ptr() for p in c["pools"]], dtype=torch.int64, device=dev)
+    k0, v0 = c["pools"][0][0].clone(), c["pools"][0][1].clone()
+    cs = cos_sin_table(2049, dev)
+    o2, r2 = torch.empty_like(c["x"]), torch.empty_like(c["x"])
+    cf.llama_decoder_layer_batch_decode_sglang(o2, r2, c["x"], c["res"], weights["wqkv"], wo, c["indptr"], c["indices"], kptrs, vptrs,
+                                               0, weights["g1"], EPS, c["positions"], cs)
+    ro2, _, _, _, _ = LO.llama_attn_block_batch_fp32(c["x"], c["res"], weights["wqkv"], wo, k0, v0, c["indptr"], c["indices"],
+                                                     c["positions"], cs, weights["g1"], EPS)
+    close(o2, ro2, "attention block output")
+    assert cf.device_status() == 0
+
+
 def test_batch_equals_batch1_block(cuda_device, weights):
     """The batched entry point at batch 1 against the batch-1 fused block (llama_decoder_layer_sglang) on the same
     sequence: same result within the parity bar (the two differ in where activations are rounded to fp16)."""
