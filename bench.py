@@ -626,8 +626,9 @@ def run_prefill(args):
 
 def run_llama_stack(args):
     """Secondary line: one decode step at batch 1 through a Llama-2-7B-shaped stack of --layers layers
-    (attention block + SwiGLU MLP block per layer, 64 launches replayed as one CUDA graph), every
-    layer with its own --llama-ctx rows of KV cache."""
+    (attention block + SwiGLU MLP block per layer), every layer with its own --llama-ctx rows of KV cache.  The 2 x
+    layers blocks of a step are launched one by one and replayed as one CUDA graph; --llama-one-launch runs them as ONE
+    persistent launch (cf_batch_begin / cf_batch_end)."""
     import clusterfusionplus_b200 as cf
 
     dev = torch.device("cuda", 0)
@@ -645,7 +646,7 @@ def run_llama_stack(args):
     ang = torch.rand(D // 2, generator=g, device=dev) * (2 * torch.pi)
     cos, sin = torch.cat([ang.cos(), ang.cos()]).contiguous(), torch.cat([ang.sin(), ang.sin()]).contiguous()
     x0, r0 = rand_half((1, H), g, dev, std=1.0), rand_half((1, H), g, dev, std=1.0)
-    stack = cf.LlamaLayerStack(layers, eps=1e-5)
+    stack = cf.LlamaLayerStack(layers, eps=1e-5, one_launch=args.llama_one_launch)
 
     def step():
         stack.step(x0, r0, cos, sin)
@@ -683,7 +684,7 @@ def run_llama_stack(args):
                    "l2": "per-step working set far larger than L2"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": src,
                      "algorithmic_bytes_per_step": per_layer * L, "traffic": None},
-        "gpu_launches": 2 * L * args.steps, "clocks": clocks, "device_status": cf.device_status(),
+        "gpu_launches": (1 if args.llama_one_launch else 2 * L) * args.steps, "clocks": clocks, "device_status": cf.device_status(),
     }))
 
 
@@ -793,6 +794,7 @@ def main():
                          "graph_decode_step API in the reference's decode loop, captured in a CUDA graph (1 GPU)")
     ap.add_argument("--batch", type=int, default=1,
                     help="with --llama-ctx: decode sequences per step; > 1 (or --llama-batched) uses the batched, paged blocks")
+    ap.add_argument("--llama-one-launch", action="store_true", help="with --llama-ctx at batch 1: all blocks of a step as one launch")
     ap.add_argument("--llama-batched", action="store_true", help="with --llama-ctx: the batched, paged blocks even at batch 1")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="instead of decode: time prompt ingestion of this many tokens (1 GPU; a secondary line)")

@@ -70,6 +70,9 @@ SIGNATURES = {
                                                        C.c_int64, C.c_void_p]),
     "cf_llama_mlp_batch_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "cf_llama_mlp_sglang": (C.c_int, [C.c_void_p] * 5 + [C.c_float, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "cf_batch_begin": (C.c_int, []),
+    "cf_batch_end": (C.c_int, [C.c_void_p]),
+    "cf_batch_abort": (C.c_int, []),
     "cf_debug_run_phases": (C.c_int, [C.c_int, _P(CfLayerWeights), _P(CfLayerIO), C.c_int64, C.c_int, C.c_void_p]),
     "cf_debug_set_trace": (C.c_int, [C.c_void_p, C.c_int64]),
     "cf_debug_set_llama_batch_trace": (C.c_int, [C.c_void_p, C.c_int64]),

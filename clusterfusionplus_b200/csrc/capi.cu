@@ -185,6 +185,16 @@ const void* kernel_ptr(int D, int cs) {
     return nullptr;
 }
 
+// several parameter blocks as one launch (head_dim 128 only: the Llama blocks)
+const void* multi_kernel_ptr(int D, int cs) {
+    if (D == 128) {
+        if (cs == 1) return reinterpret_cast<const void*>(&fused_decode_multi_kernel<128, 1>);
+        if (cs == 2) return reinterpret_cast<const void*>(&fused_decode_multi_kernel<128, 2>);
+        if (cs == 4) return reinterpret_cast<const void*>(&fused_decode_multi_kernel<128, 4>);
+    }
+    return nullptr;
+}
+
 struct DescKey {
     const void* p[14];
     int64_t kv_rows;
@@ -210,6 +220,16 @@ struct DeviceState {
     LaunchCfg cfg[2];  // [0]: head_dim 80, [1]: head_dim 128
     Workspace ws;
     std::map<DescKey, LayerDesc*> desc_cache;
+    // batches of recorded launches (cf_batch_begin / cf_batch_end): parameter blocks on the device, what they hold,
+    // two pinned staging slots with the events of their last copies, the grid barrier's two words
+    Params* multi_dev = nullptr;
+    size_t multi_cap = 0;
+    std::vector<Params> multi_last;
+    Params* multi_pin[2] = {nullptr, nullptr};
+    cudaEvent_t multi_ev[2] = {nullptr, nullptr};
+    int multi_slot = 0;
+    unsigned* multi_bar = nullptr;
+    bool multi_attr[3] = {false, false, false};
     std::map<std::pair<int, int64_t>, GraphCtx> contexts;
     unsigned long long* trace = nullptr;  // diagnostics: timeline buffer applied to every launch
     size_t trace_slots = 0;
@@ -320,6 +340,16 @@ int check_dims(const CfDims& d) {
 }
 
 // ring depth and activation buffer for one launch
+// cf_batch_begin .. cf_batch_end on this thread: launch() records the finished parameter block instead of launching
+struct Recorded {
+    Params p;
+    size_t smem;
+    int head_dim, cs, grid;
+};
+thread_local bool tl_recording = false;
+thread_local std::vector<Recorded> tl_rec;
+constexpr size_t MULTI_PARAMS_SLOT = (sizeof(Params) + 127) / 128 * 128;  // the blocks' copy in shared memory
+
 int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* nstage, int* xbuf_floats, int* aux_off) {
     const int KVW = d.heads * d.head_dim;
     const int kco = (p3_flags & F3_USE_O) ? ceil_div(KVW, KCHUNK) : 0;
@@ -341,7 +371,8 @@ int fit_smem(const DeviceState& ds, const CfDims& d, int cs, int p3_flags, int* 
     *aux_off = aux;
     xb = (xb + 3) / 4 * 4;
     const long fixed = static_cast<long>(smem_bytes_for(0, xb));
-    int ns = static_cast<int>((ds.smem_optin - fixed) / STAGE_BYTES);
+    const long avail = ds.smem_optin - (tl_recording ? static_cast<long>(MULTI_PARAMS_SLOT) + 128 : 0);
+    int ns = static_cast<int>((avail - fixed) / STAGE_BYTES);
     const int cap = env_int("CFB200_STAGES", 0);
     if (cap > 0 && ns > cap) ns = cap;
     if (ns > MAX_STAGES) ns = MAX_STAGES;
@@ -407,6 +438,21 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
     p.pdl = (env_int("CFB200_PDL", 0) != 0 && !(p.phase_mask & PH_P4) && p.tp_size <= 1) ? 1 : 0;
     p.merge_seg_max = env_int("CFB200_MERGE_SEG", 0);
     p.trace = nullptr;
+    if (tl_recording) {
+        if ((p.phase_mask & PH_P4) || p.tp_size > 1)
+            return fail(CF_ERR_UNSUPPORTED, "whole-token and tensor-parallel launches cannot be part of a batch");
+        if (!multi_kernel_ptr(d.head_dim, c.cs)) return fail(CF_ERR_UNSUPPORTED, "batches need head_dim 128");
+        if (tl_rec.size() >= 4096) return fail(CF_ERR_UNSUPPORTED, "more than 4096 launches in one batch");
+        p.pdl = 0;
+        Recorded r;
+        r.p = p;
+        r.smem = smem;
+        r.head_dim = d.head_dim;
+        r.cs = c.cs;
+        r.grid = c.grid;
+        tl_rec.push_back(r);
+        return CF_OK;
+    }
     if (ds.trace && static_cast<size_t>(c.grid) * (p.n_layers + 1) * TRACE_EVENTS <= ds.trace_slots) p.trace = ds.trace;
     for (int attempt = 0; attempt < 2; ++attempt) {
         cudaLaunchConfig_t lc = {};
@@ -946,6 +992,122 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
     p.sin = sin;
     p.seq_host = static_cast<int>(seq_len);
     return launch(*ds, d, p, st);
+}
+
+int cf_batch_begin(void) {
+    if (tl_recording) return fail(CF_ERR_INVALID, "cf_batch_begin: a batch is already open on this thread");
+    tl_rec.clear();
+    tl_recording = true;
+    return CF_OK;
+}
+
+int cf_batch_abort(void) {
+    tl_recording = false;
+    tl_rec.clear();
+    return CF_OK;
+}
+
+int cf_batch_end(void* stream) {
+    if (!tl_recording) return fail(CF_ERR_INVALID, "cf_batch_end without cf_batch_begin");
+    tl_recording = false;
+    std::vector<Recorded> rec;
+    rec.swap(tl_rec);
+    if (rec.empty()) return CF_OK;
+    DeviceState* ds;
+    int rc = get_device(&ds);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int n = static_cast<int>(rec.size());
+    size_t smem = 0;
+    for (const Recorded& r : rec) {
+        if (r.head_dim != rec[0].head_dim || r.cs != rec[0].cs || r.grid != rec[0].grid)
+            return fail(CF_ERR_UNSUPPORTED, "the launches of a batch must share head_dim and launch geometry");
+        if (r.smem > smem) smem = r.smem;
+    }
+    const size_t params_off = align_up(smem, 128);
+    const size_t dyn = params_off + MULTI_PARAMS_SLOT;
+    if (dyn > static_cast<size_t>(ds->smem_optin))
+        return fail(CF_ERR_UNSUPPORTED, "batch needs %zu bytes of shared memory (%d available)", dyn, ds->smem_optin);
+    const void* fn = multi_kernel_ptr(rec[0].head_dim, rec[0].cs);
+    std::lock_guard<std::mutex> lk(g_mu);
+    const int ai = rec[0].cs == 1 ? 0 : (rec[0].cs == 2 ? 1 : 2);
+    if (!ds->multi_attr[ai]) {
+        CF_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, ds->smem_optin));
+        ds->multi_attr[ai] = true;
+    }
+    // the blocks on the device: uploaded only when they differ from what is there (a captured graph replays an
+    // identical batch without any copy; a batch that differs cannot be captured)
+    bool same = ds->multi_last.size() == rec.size();
+    for (int i = 0; same && i < n; ++i) same = memcmp(&ds->multi_last[i], &rec[i].p, sizeof(Params)) == 0;
+    if (!same) {
+        if ((rc = refuse_upload_in_capture(st, "a batch whose parameters changed"))) return rc;
+        if (static_cast<size_t>(n) > ds->multi_cap) {
+            const size_t cap = align_up(static_cast<size_t>(n), 64);
+            CF_CUDA(cudaDeviceSynchronize());  // earlier batches may still read the old buffers
+            if (ds->multi_dev) cudaFree(ds->multi_dev);
+            for (int k = 0; k < 2; ++k) {
+                if (ds->multi_pin[k]) cudaFreeHost(ds->multi_pin[k]);
+                ds->multi_pin[k] = nullptr;
+                if (!ds->multi_ev[k]) CF_CUDA(cudaEventCreateWithFlags(&ds->multi_ev[k], cudaEventDisableTiming));
+            }
+            ds->multi_dev = nullptr;
+            ds->multi_cap = 0;
+            CF_CUDA(cudaMalloc(&ds->multi_dev, cap * sizeof(Params)));
+            for (int k = 0; k < 2; ++k) CF_CUDA(cudaMallocHost(&ds->multi_pin[k], cap * sizeof(Params)));
+            ds->multi_cap = cap;
+        }
+        if (!ds->multi_bar) {
+            CF_CUDA(cudaMalloc(&ds->multi_bar, 256));
+            CF_CUDA(cudaMemset(ds->multi_bar, 0, 256));
+        }
+        const int slot = ds->multi_slot;
+        ds->multi_slot ^= 1;
+        CF_CUDA(cudaEventSynchronize(ds->multi_ev[slot]));  // the copy that last read this staging slot is over
+        for (int i = 0; i < n; ++i) ds->multi_pin[slot][i] = rec[i].p;
+        CF_CUDA(cudaMemcpyAsync(ds->multi_dev, ds->multi_pin[slot], static_cast<size_t>(n) * sizeof(Params),
+                                cudaMemcpyHostToDevice, st));
+        CF_CUDA(cudaEventRecord(ds->multi_ev[slot], st));
+        ds->multi_last.resize(n);
+        for (int i = 0; i < n; ++i) ds->multi_last[i] = rec[i].p;
+    }
+    MultiArgs ma;
+    ma.blocks = ds->multi_dev;
+    ma.n_blocks = n;
+    ma.params_off = static_cast<int>(params_off);
+    ma.bar = ds->multi_bar;
+    ma.status = ds->ws.status;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(rec[0].grid);
+    lc.blockDim = dim3(NTHREADS);
+    lc.dynamicSmemBytes = dyn;
+    lc.stream = st;
+    cudaLaunchAttribute at[2];
+    int na = 0;
+    if (rec[0].cs > 1) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = rec[0].cs;
+        at[na].val.clusterDim.y = 1;
+        at[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    LaunchCfg& c = ds->cfg[rec[0].head_dim == 128];
+    if (c.coop) {
+        at[na].id = cudaLaunchAttributeCooperative;
+        at[na].val.cooperative = 1;
+        ++na;
+    }
+    lc.attrs = at;
+    lc.numAttrs = na;
+    void* args[1] = {&ma};
+    cudaError_t e = cudaLaunchKernelExC(&lc, fn, args);
+    if (e != cudaSuccess && c.coop) {
+        (void)cudaGetLastError();
+        lc.numAttrs = na - 1;  // without the cooperative attribute: the grid is sized from the occupancy query
+        e = cudaLaunchKernelExC(&lc, fn, args);
+    }
+    if (e != cudaSuccess)
+        return fail(CF_ERR_CUDA, "batch launch failed: %s (%d blocks, grid %d, smem %zu)", cudaGetErrorString(e), n, rec[0].grid, dyn);
+    return CF_OK;
 }
 
 int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,

@@ -1146,13 +1146,15 @@ __device__ __forceinline__ void merge_sums(const MergeArgs& a, int t, int nthr, 
     }
 }
 
+// The whole launch of one parameter block: every thread of the CTA calls it.  `kv_maps` is the address of
+// Params::kv_maps in memory the TMA unit can read a tensor map from (kernel parameters or global memory -- not the
+// shared-memory copy of the parameters that a multi-block launch works from).
 template <int D, int CS>
-__global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_constant__ Params p) {
+__device__ __forceinline__ void decode_body(const Params& p, const CUtensorMap* kv_maps, uint8_t* smem_raw) {
     static_assert(D % 8 == 0 && D <= 128, "head_dim must be a multiple of 8, at most 128");
     // one attention partial: D numerators, running max, denominator, padded so that every
     // record (and every 4-element group in it) starts on a 16-byte boundary
     constexpr int PREC = D + 4;
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const Smem sm = carve(smem_raw, p.nstage, p.xbuf_floats);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, cta = blockIdx.x;
@@ -1326,8 +1328,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
                 }
                 pr.depend();  // key / value tiles and everything after them may come from the preceding kernel
                 if (p.phase_mask & PH_P2) {
-                    const CUtensorMap* tmk = p.kv_inline ? &p.kv_maps[0] : &L->tm_k;
-                    const CUtensorMap* tmv = p.kv_inline ? &p.kv_maps[1] : &L->tm_v;
+                    const CUtensorMap* tmk = p.kv_inline ? kv_maps : &L->tm_k;
+                    const CUtensorMap* tmv = p.kv_inline ? kv_maps + 1 : &L->tm_v;
                     for (int t = t2a; t < t2b; ++t) pr.kv_stage<D>(tmk, tmv, t / nch, t % nch);
                     trace_mark(p, cta, l, TR_PROD_P2);
                 }
@@ -2233,6 +2235,80 @@ __global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_
     // no CTA leaves while a peer may still store into its shared memory
     __syncthreads();
     if constexpr (CS > 1) dsm::cluster_sync_all();
+}
+
+template <int D, int CS>
+__global__ void __launch_bounds__(NTHREADS, 1) fused_decode_kernel(const __grid_constant__ Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    decode_body<D, CS>(p, p.kv_maps, smem_raw);
+}
+
+// Several parameter blocks as ONE launch (a stack of layers whose blocks differ in kind: the Llama attention
+// and SwiGLU MLP blocks), in order.  Each block runs exactly as its own launch would -- barriers initialised,
+// work split derived, epochs read -- from a copy of its parameters in shared memory; between two blocks all CTAs
+// meet at a sense-reversing grid barrier (bar[0] arrivals, bar[1] generation), which orders the next block
+// behind everything the previous one wrote, its bookkeeping words included.  What a launch boundary costs beyond
+// that (drain, launch, CTA start-up) is gone.
+struct MultiArgs {
+    const Params* blocks;   // [n_blocks] in global memory
+    int n_blocks;
+    int params_off;         // byte offset of the parameter copy inside dynamic shared memory (beyond every block's own use)
+    unsigned* bar;          // two words, zero before the first launch
+    int* status;
+};
+template <int D, int CS>
+__global__ void __launch_bounds__(NTHREADS, 1) fused_decode_multi_kernel(const __grid_constant__ MultiArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    static_assert(sizeof(Params) % 16 == 0, "the parameter block is copied in 16-byte pieces");
+    Params* sp = reinterpret_cast<Params*>(smem_raw + a.params_off);
+    const int tid = threadIdx.x;
+    for (int b = 0; b < a.n_blocks; ++b) {
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(a.blocks + b);
+            uint4* dst = reinterpret_cast<uint4*>(sp);
+            for (int i = tid; i < static_cast<int>(sizeof(Params) / 16); i += NTHREADS) dst[i] = __ldg(src + i);
+        }
+        __syncthreads();
+        decode_body<D, CS>(*sp, a.blocks[b].kv_maps, smem_raw);
+        // every thread is out of the block; peers' remote arrivals have landed before the barriers are re-made
+        __syncthreads();
+        if constexpr (CS > 1) dsm::cluster_sync_all();
+        if (tid == 0) {
+            // the next block initialises its barriers afresh: invalidate this block's first
+            const Smem sm = carve(smem_raw, sp->nstage, sp->xbuf_floats);
+            for (int s = 0; s < sp->nstage; ++s) {
+                mbar_inval(smem_u32(sm.full + s));
+                mbar_inval(smem_u32(sm.empty + s));
+            }
+            for (int i = 0; i < 9; ++i) mbar_inval(smem_u32(sm.xbar + i));
+        }
+        __syncthreads();
+        if (b + 1 < a.n_blocks) {
+            if (tid == 0) {
+                const unsigned gen = ld_acquire_u32(a.bar + 1);
+                __threadfence();
+                const unsigned old = atomicAdd(a.bar, 1u);
+                if (old == gridDim.x - 1u) {
+                    a.bar[0] = 0u;
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.bar + 1), "r"(gen + 1u) : "memory");
+                } else {
+                    // bounded like every wait of this kernel: on a timeout the status word says so and the
+                    // remaining blocks run on (their own waits will give up as well)
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (ld_acquire_u32(a.bar + 1) == gen) {
+                        __nanosleep(64);
+                        if (globaltimer_ns() - t0 > wait_limit_ns(ST_TIMEOUT_GRID)) {
+                            atomicCAS(a.status, 0, ST_TIMEOUT_GRID);
+                            break;
+                        }
+                    }
+                }
+                __threadfence();
+            }
+            __syncthreads();
+        }
+    }
 }
 
 }  // namespace cfb

@@ -23,9 +23,14 @@ class LlamaLayerStack:
     k_cache / v_cache [seq,H] (read-only history), gate_up_weight [2F,H] (gate rows first),
     down_weight [H,F], rms_post_weight [H]."""
 
-    def __init__(self, layers: Sequence[Dict[str, torch.Tensor]], eps: float = 1e-5):
+    def __init__(self, layers: Sequence[Dict[str, torch.Tensor]], eps: float = 1e-5, one_launch: bool = False):
         self.layers: List[Dict[str, torch.Tensor]] = list(layers)
         self.eps = float(eps)
+        # one_launch: the 2 x layers block calls of a step are recorded (cf_batch_begin / cf_batch_end) and run as
+        # ONE persistent launch with grid barriers between the blocks, instead of one launch per block.  Same bits;
+        # measured slower than the per-block launches replayed from a CUDA graph (3 880 against 3 389 us for 32
+        # layers), so it is off unless asked for
+        self.one_launch = bool(one_launch)
         dev = self.layers[0]["weight_qkv"].device
         opts = dict(dtype=torch.float16, device=dev)
         self.x = [torch.zeros(1, H, **opts) for _ in range(2)]
@@ -53,11 +58,20 @@ class LlamaLayerStack:
         cp, sp = _req(cos, "cos", D, torch.float32, exact=False), _req(sin, "sin", D, torch.float32, exact=False)
         xa, ra, xb, rb = self.x[0], self.r[0], self.x[1], self.r[1]
         x_in, r_in = _req(hidden, "hidden", H), _req(residual, "residual", H)
-        for i, (wqkv, wo, kp, vp, rows, g1, wgu, wd, g2, ffn) in enumerate(self._args):
-            check(lib.cf_llama_decoder_layer_sglang(x_in, r_in, wqkv, wo, kp, vp, rows, g1, self.eps, cp, sp,
-                                                    xb.data_ptr(), rb.data_ptr(), self.k_new[i].data_ptr(),
-                                                    self.v_new[i].data_ptr(), st))
-            check(lib.cf_llama_mlp_sglang(xb.data_ptr(), rb.data_ptr(), wgu, wd, g2, self.eps, ffn, xa.data_ptr(),
-                                          ra.data_ptr(), st))
-            x_in, r_in = xa.data_ptr(), ra.data_ptr()
+        if self.one_launch:
+            check(lib.cf_batch_begin())
+        try:
+            for i, (wqkv, wo, kp, vp, rows, g1, wgu, wd, g2, ffn) in enumerate(self._args):
+                check(lib.cf_llama_decoder_layer_sglang(x_in, r_in, wqkv, wo, kp, vp, rows, g1, self.eps, cp, sp,
+                                                        xb.data_ptr(), rb.data_ptr(), self.k_new[i].data_ptr(),
+                                                        self.v_new[i].data_ptr(), st))
+                check(lib.cf_llama_mlp_sglang(xb.data_ptr(), rb.data_ptr(), wgu, wd, g2, self.eps, ffn, xa.data_ptr(),
+                                              ra.data_ptr(), st))
+                x_in, r_in = xa.data_ptr(), ra.data_ptr()
+        except Exception:
+            if self.one_launch:
+                lib.cf_batch_abort()
+            raise
+        if self.one_launch:
+            check(lib.cf_batch_end(st))
         return xa, ra

@@ -156,6 +156,21 @@ int cf_llama_decoder_layer_sglang(const void* input, const void* residual, const
 int cf_llama_mlp_sglang(const void* input, const void* residual, const void* gate_up_weight, const void* down_weight,
                         const void* rms_weight, float eps, int64_t ffn, void* output, void* residual_out, void* stream);
 
+/* Several layer-level calls as ONE launch.  Between cf_batch_begin() and cf_batch_end(stream) the layer-level
+ * entry points called on this thread (cf_pythia_*, cf_*_graph_decode_step, cf_llama_decoder_layer_sglang,
+ * cf_llama_mlp_sglang; head_dim 128 models) validate and prepare their launch as usual but do not launch; their
+ * stream arguments are ignored.  cf_batch_end launches one persistent kernel on `stream` that runs the recorded
+ * blocks in call order, each exactly as its own launch would have run, with a grid barrier in between: what a
+ * launch boundary costs beyond that is gone (a 32-layer Llama stack is 64 blocks).  The blocks' parameters are
+ * uploaded only when they differ from the previous batch's, so an unchanged batch can be captured into a CUDA
+ * graph; one that changed is refused during capture (CF_ERR_UNSUPPORTED).  cf_batch_abort() drops an open batch.
+ * Calls that cannot be part of a batch (the whole-token decoder, tensor-parallel launches, the batched Llama
+ * blocks, which are another kernel) fail or launch at once as documented for them.  The reference has no
+ * counterpart: its callers pay one launch per layer (tests/benchmark_decode_6b9.py:133-198). */
+int cf_batch_begin(void);
+int cf_batch_end(void* stream);
+int cf_batch_abort(void);
+
 /* Llama-2-7B attention block for a BATCH of 1..16 decode sequences over a paged KV pool, one launch.
  * Per sequence b: residual_output[b] = input[b] + residual[b] (fp16; residual may be NULL);
  * h = RMSNorm(residual_output[b], rms_input_weight, eps); q,k,v = weight_qkv h (rows [Q of all heads;

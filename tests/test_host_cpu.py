@@ -93,6 +93,19 @@ def test_transposed_llama_entry_point_is_a_documented_refusal():
         clusterfusion.llama_decoder_layer(*[None] * 8)
 
 
+def test_batch_recording_state_machine_without_gpu():
+    """cf_batch_begin / cf_batch_end / cf_batch_abort: misuse is reported, an empty batch is a no-op."""
+    from clusterfusionplus_b200 import _lib
+    lib = _lib.lib
+    assert lib.cf_batch_end(None) != 0 and "cf_batch_begin" in _lib.last_error()
+    assert lib.cf_batch_begin() == 0
+    assert lib.cf_batch_begin() != 0 and "already open" in _lib.last_error()
+    assert lib.cf_batch_abort() == 0
+    assert lib.cf_batch_begin() == 0
+    assert lib.cf_batch_end(None) == 0          # nothing recorded: nothing to launch, no device needed
+    assert lib.cf_batch_end(None) != 0
+
+
 def test_cpu_tensors_are_rejected():
     import clusterfusion
     H, F = 2560, 10240

@@ -143,16 +143,32 @@ def test_llama_layer_stack_two_layers_vs_oracle(cuda_device):
     assert_close(res, ro, "stack residual")
 
 
-def test_llama_layer_stack_class_matches_block_calls(cuda_device):
-    """LlamaLayerStack (ping-pong buffers, no copies) gives bit-identical results to chaining the two block calls."""
+@pytest.mark.parametrize("one_launch", [False, True], ids=["per-block", "one-launch"])
+def test_llama_layer_stack_class_matches_block_calls(cuda_device, one_launch):
+    """LlamaLayerStack (ping-pong buffers, no copies) gives bit-identical results to chaining the two block calls --
+    launched block by block, and with all blocks of the step recorded and run as ONE persistent launch
+    (cf_batch_begin / cf_batch_end: grid barriers between the blocks), twice (the second batch is identical and
+    needs no upload) and captured into a CUDA graph."""
     import clusterfusion as cf
     seq, ffn = 129, 11008
     blocks = [(make(seq, cuda_device, seed=40 + i), make_mlp(ffn, cuda_device, seed=50 + i)) for i in range(3)]
     layers = [dict(weight_qkv=a["wqkv"], weight_o=a["wo"], rms_input_weight=a["g"], k_cache=a["k"], v_cache=a["v"],
                    gate_up_weight=m["wgu"], down_weight=m["wd"], rms_post_weight=m["g"]) for a, m in blocks]
     a0 = blocks[0][0]
-    stack = cf.LlamaLayerStack(layers, eps=1e-5)
+    stack = cf.LlamaLayerStack(layers, eps=1e-5, one_launch=one_launch)
     xs, rs = stack.step(a0["x"], a0["res"], a0["cos"], a0["sin"])
+    if one_launch:
+        first = (xs.clone(), rs.clone())
+        xs, rs = stack.step(a0["x"], a0["res"], a0["cos"], a0["sin"])
+        assert torch.equal(xs, first[0]) and torch.equal(rs, first[1])
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            stack.step(a0["x"], a0["res"], a0["cos"], a0["sin"])
+        xs.zero_(), rs.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(xs, first[0]) and torch.equal(rs, first[1])
     x, res = a0["x"].clone(), a0["res"].clone()
     for i, (a, m) in enumerate(blocks):
         x, res, kn, vn = cf.llama_decoder_layer_sglang(x, res, a["wqkv"], a["wo"], a["k"], a["v"], a["g"], 1e-5, a0["cos"], a0["sin"])
