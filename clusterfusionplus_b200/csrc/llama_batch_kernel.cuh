@@ -19,8 +19,11 @@
 //     silu(gate) * up, fp16 output);
 //   * tcgen05.commit hands a ring stage back to the TMA producer when the MMAs that read it are done.
 //
-// The output rows of every projection are split over all CTAs in 8-row granules (no split-K), so the
-// sums have a fixed order and nothing is atomic.  Attention streams each sequence's cached rows
+// The output rows of every projection are split over all CTAs in 8-row granules.  The two narrow projections
+// (O and down: under 40 rows per CTA, bound by the NUMBER of MMAs) are in addition cut along K over groups of CTAs:
+// fp32 partial outputs in global memory, a grid barrier, the slices added in slice order.  The merged [gate; up]
+// matrix is fetched through a 4-D map, so that one copy brings a K block's gate rows followed by its up rows: one
+// B operand.  Every sum has a fixed order and nothing is atomic.  Attention streams each sequence's cached rows
 // through the page table (the pool row of token t of sequence b is indices[indptr[b] + t], one row =
 // one token, as in the reference's `paged_kv_indices[...] * HIDDEN_DIM` addressing, :343-371) with one
 // 256-byte run of asynchronous copies per (row, head), in items of 128 rows spread evenly over the CTAs; partial (max,
