@@ -103,6 +103,8 @@ SIGNATURES = {
     "cf_debug_noalloc_scratch": (C.c_int, [_P(C.c_void_p), _P(C.c_int64), _P(C.c_int64)]),
     "cf_prefill_linear": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                     C.c_int64, C.c_int, C.c_void_p]),
+    "cf_prefill_layernorm2": (C.c_int, [C.c_void_p] * 7 + [C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
+    "cf_prefill_rope_split": (C.c_int, [C.c_void_p] * 6 + [C.c_int64] * 5 + [C.c_void_p]),
 }
 
 

@@ -2,9 +2,10 @@
 
     python clusterfusionplus_b200/build.py [--force] [--verbose]
 
-Three translation units, compiled separately (objects cached under lib/obj/) and linked into one
+Four translation units, compiled separately (objects cached under lib/obj/) and linked into one
 shared library: the decode kernel with the C ABI, the batched Llama decode blocks (hand-written
-tcgen05 skinny GEMMs + paged attention), and the tensor-core prefill GEMM, which is built from the CUTLASS / CuTe headers found in the Python environment (the `flashinfer` wheel
+tcgen05 skinny GEMMs + paged attention), the elementwise kernels of the prompt pass, and the tensor-core prefill
+GEMM, which is built from the CUTLASS / CuTe headers found in the Python environment (the `flashinfer` wheel
 vendors them; set CUTLASS_INCLUDE to use another copy).  The library has no torch dependency;
 it links the CUDA runtime statically and finds the driver's tensor-map encoder at run time.
 """
@@ -28,6 +29,7 @@ UNITS = {
     "capi.cu": (["decode_kernel.cuh", "pipeline.cuh", "dsm.cuh", "prefill_gemm.h", "host_common.h", HEADER], False),
     "llama_batch.cu": (["llama_batch_kernel.cuh", "pipeline.cuh", "host_common.h", HEADER], False),
     "prefill_gemm.cu": (["prefill_gemm.h"], True),
+    "prefill_ops.cu": (["host_common.h", HEADER], False),
 }
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -159,8 +159,9 @@ class PythiaDecoder:
     def prefill(self, tokens: Sequence[int]) -> None:
         """Ingest a prompt.  Rows [0, n-1) of every cache are computed for all prompt positions
         at once: the four linear layers of a block run as tensor-core GEMMs with their bias,
-        GELU and residual fused (cf_prefill_linear); LayerNorm, RoPE and the causal attention
-        over the prompt are torch library kernels.  The reference has no prefill of its own and
+        GELU and residual fused (cf_prefill_linear), both LayerNorms as one kernel (cf_prefill_layernorm2), RoPE
+        and the cache rows as another (cf_prefill_rope_split); the causal attention over the prompt is torch's
+        library kernel.  The reference has no prefill of its own and
         leaves it to the HuggingFace model (tests/benchmark_full.py:195-199).  The decoder is
         then positioned on the last prompt token, so the next step() consumes it through the
         fused decode kernel and yields the first generated token."""
@@ -173,27 +174,26 @@ class PythiaDecoder:
             d = self.dims
             H, NH, D, R = d.hidden, d.heads, d.head_dim, d.rotary
             gelu = CF_ACT_GELU_ERF if (self.flags & CF_DECODER_GELU_ERF) else CF_ACT_GELU_TANH
-            cos, sin = self.cos[:m, None, :], self.sin[:m, None, :]  # [m, 1, R] fp32
-
-            def rope(t):  # [m, NH, D] fp16 -> rotate-half on the first R dims, fp32 math
-                r = t[..., :R].float()
-                half = torch.cat([-r[..., R // 2:], r[..., : R // 2]], dim=-1)
-                return torch.cat([(r * cos + half * sin).to(t.dtype), t[..., R:]], dim=-1)
-
-            def norm(x, w, b):
-                return F.layer_norm(x.float(), (H,), w.float(), b.float(), 1e-5).to(x.dtype)
-
+            st = torch.cuda.current_stream().cuda_stream
+            KVW = NH * D
+            cos_p, sin_p = _req(self.cos, "cos", m * R, torch.float32, exact=False), _req(self.sin, "sin", m * R, torch.float32, exact=False)
             x = self.head["embed_in"][ids[:m]].contiguous()
+            y1, y2 = torch.empty_like(x), torch.empty_like(x)
+            q = torch.empty(m, NH, D, device=self.device, dtype=torch.float16)
             for w, (kc, vc) in zip(self.layers, self.caches):
-                y1 = norm(x, w["ln_weight"].reshape(-1), w["ln_bias"].reshape(-1))
-                qkv = prefill_linear(y1, w["qkv_weight"], w["qkv_bias"]).view(m, NH, 3, D)
-                q, k, v = rope(qkv[:, :, 0]), rope(qkv[:, :, 1]), qkv[:, :, 2]
-                kc[:m] = k.reshape(m, NH * D)
-                vc[:m] = v.reshape(m, NH * D)
+                # both LayerNorms of the block in one pass over x (cf_prefill_layernorm2)
+                check(lib.cf_prefill_layernorm2(x.data_ptr(), _req(w["ln_weight"], "ln_weight", H), _req(w["ln_bias"], "ln_bias", H),
+                                                _req(w["post_ln_weight"], "post_ln_weight", H),
+                                                _req(w["post_ln_bias"], "post_ln_bias", H), y1.data_ptr(), y2.data_ptr(), m, H,
+                                                1e-5, st))
+                qkv = prefill_linear(y1, w["qkv_weight"], w["qkv_bias"])          # [m, NH, 3, D]
+                # rotated queries, rotated keys and values straight into the caches' first m rows (cf_prefill_rope_split)
+                check(lib.cf_prefill_rope_split(qkv.data_ptr(), cos_p, sin_p, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), m, NH, D, R,
+                                                KVW, st))
+                k, v = kc[:m].view(m, NH, D), vc[:m].view(m, NH, D)
                 attn = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
                                                       v.transpose(0, 1)[None], is_causal=True)
                 attn = attn[0].transpose(0, 1).reshape(m, NH * D).contiguous()
-                y2 = norm(x, w["post_ln_weight"].reshape(-1), w["post_ln_bias"].reshape(-1))
                 mid = prefill_linear(y2, w["mlp_up_weight"], w["mlp_up_bias"], act=gelu)
                 # parallel residual: x + attention branch, then + MLP branch, each add in a GEMM epilogue
                 h = prefill_linear(attn, w["o_weight"], w["o_bias"], residual=x)

@@ -380,6 +380,20 @@ int cf_decoder_destroy(int64_t handle);
 int cf_prefill_linear(const void* x, const void* weight, const void* bias, const void* residual, void* out,
                       int64_t m, int64_t n, int64_t k, int act, void* stream);
 
+/* The rest of a GPT-NeoX block's prompt pass that is not a GEMM or the causal attention, as two kernels.
+ * cf_prefill_layernorm2: y1 = LayerNorm(x; gamma1, beta1) and, when y2 != NULL, y2 = LayerNorm(x; gamma2, beta2)
+ * for m rows of `hidden` fp16 values in ONE pass over x (the input and post-attention norms of a parallel-residual
+ * block see the same x and share mean and variance); fp32 statistics, two-pass, eps as given.
+ * cf_prefill_rope_split: qkv [m][heads][3][head_dim] (the fused projection's per-head q, k, v order) ->
+ * q_out [m][heads][head_dim] with rotate-half RoPE on the first `rotary` dims, the rotated keys into
+ * k_rows[i * kv_row_stride ...] and the values into v_rows[i * kv_row_stride ...] (the caches' first m rows);
+ * row i is position i; cos / sin are [m][rotary] fp32.  Same arithmetic as the decode kernel's, so a cache filled
+ * here matches one filled token by token.  Asynchronous on `stream`. */
+int cf_prefill_layernorm2(const void* x, const void* gamma1, const void* beta1, const void* gamma2, const void* beta2,
+                          void* y1, void* y2, int64_t m, int64_t hidden, float eps, void* stream);
+int cf_prefill_rope_split(const void* qkv, const float* cos, const float* sin, void* q_out, void* k_rows, void* v_rows,
+                          int64_t m, int64_t heads, int64_t head_dim, int64_t rotary, int64_t kv_row_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
