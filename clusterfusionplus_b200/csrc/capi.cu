@@ -391,7 +391,7 @@ int launch(DeviceState& ds, const CfDims& d, Params& p, cudaStream_t st) {
         return fail(CF_ERR_UNSUPPORTED, "hidden %d too wide for %d clusters", d.hidden, c.grid / c.cs);
     {
         const int kco = ceil_div(d.heads * d.head_dim, KCHUNK);
-        const int hpc = ceil_div(KCHUNK, d.head_dim) + 1;
+        const int hpc = heads_per_chunk(d.head_dim);
         const int pstr = ceil_div(c.grid, d.heads) + 2;
         if (pstr > MAX_PARTS || ceil_div(kco, c.cs) * hpc * pstr > WTS_SLOTS)
             return fail(CF_ERR_UNSUPPORTED, "attention merge table too small for %d heads on %d CTAs", d.heads, c.grid);

@@ -376,6 +376,10 @@ __device__ __forceinline__ Smem carve(uint8_t* base, int nstage, int xbuf_floats
 // warps write while P1 still runs, then the hand-over buffer of attention partials (one slot per consumer
 // warp: D numerators, then NCWARP {max, denominator} pairs).  It lies behind both LayerNorm outputs (live
 // through P1) and behind the MLP chunks that P3 stages (written while a partial may still be in the buffer).
+// heads whose attention output can fall into one KCHUNK-wide chunk of P3's K range: a whole number when the chunk
+// is a multiple of the head width (head_dim 128: two), else the covering count plus one for the straddle (head_dim
+// 80: five).  The merge table has one row of partial slots per (chunk, head), so unused rows cost poll iterations.
+__host__ __device__ constexpr int heads_per_chunk(int D) { return (KCHUNK % D == 0) ? KCHUNK / D : (KCHUNK + D - 1) / D + 1; }
 __host__ __device__ __forceinline__ int aux_floats(int D) { return MAXHPC * 3 * D + NCWARP * D + 2 * NCWARP; }
 
 // ---------------------------------------------------------------- math helpers
@@ -1068,7 +1072,7 @@ struct MergeArgs {
 };
 template <int D, int CS>
 __device__ __forceinline__ void merge_sums(const MergeArgs& a, int t, int nthr, int bar_id) {
-    constexpr int HPC = (KCHUNK + D - 1) / D + 1;
+    constexpr int HPC = heads_per_chunk(D);
     const int nve = a.nve, mseg = a.mseg, pstr = a.pstr;
     const int seglen = ceil_div(ceil_div(pstr, mseg), 8) * 8;
     float4* segbuf = reinterpret_cast<float4*>(a.xbuf + a.aux_off);
@@ -1240,7 +1244,7 @@ __device__ __forceinline__ void decode_body(const Params& p, const CUtensorMap* 
     const int my3 = (KC3 > me) ? ceil_div(KC3 - me, CS) : 0;  // chunks me, me+CS, ...
     // attention merge tables (P3): my chunks that hold attention, heads touching a
     // chunk, partial slots per head
-    constexpr int HPC = (KCHUNK + D - 1) / D + 1;
+    constexpr int HPC = heads_per_chunk(D);
     const int nattn = (KCo > me) ? ceil_div(KCo - me, CS) : 0;
     const int pstr = (nch == 0) ? 1 : min(MAX_PARTS, ceil_div(G, NH) + 2);
     int NG4 = 0, g4a = 0, g4b = 0;
